@@ -73,13 +73,15 @@ class PageTableHost:
     """Pages of one cache group, per slot: logical page number -> physical page.
 
     `window` > 0 means that only the last `window` positions of a sequence are ever read, so
-    pages wholly below that range are given back after each step (`trim`)."""
+    pages wholly below that range are given back after each step (`trim`); with `keep_first` > 0 the
+    first that many positions are read for ever as well, and the pages that hold them stay."""
 
-    def __init__(self, n_pages: int, page_size: int, max_pages_per_seq: int, window: int = 0):
+    def __init__(self, n_pages: int, page_size: int, max_pages_per_seq: int, window: int = 0, keep_first: int = 0):
         self.pages = FreeList(n_pages, "page")
         self.page_size = page_size
         self.max_pages_per_seq = max_pages_per_seq
         self.window = window
+        self.keep_first = max(0, keep_first) if window > 0 else 0
         self._held: Dict[int, Dict[int, int]] = {}      # slot -> {logical page: physical page}
 
     def open_slot(self, slot: int) -> None:
@@ -115,7 +117,8 @@ class PageTableHost:
             return []
         held = self._held[slot]
         first = max(0, length + 1 - self.window) // self.page_size
-        dead = [lp for lp in held if lp < first]
+        kept = (self.keep_first + self.page_size - 1) // self.page_size      # pages of the positions kept for ever
+        dead = [lp for lp in held if kept <= lp < first]
         for lp in dead:
             self.pages.give_back(held.pop(lp))
         return dead

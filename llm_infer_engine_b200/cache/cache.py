@@ -2,14 +2,15 @@
 
 Layout. A *unit* is the storage of one entry of the model's run order (a layer that runs
 twice has two units; a layer that reads another entry's cache has none). Units whose mixers
-ask for the same thing (KV heads, head size, window) form a *group* with storage of its own:
+ask for the same thing (KV heads, head sizes, window, kept first positions) form a *group* with storage of its own:
 
     k, v          [units, pages + 1, kv_heads, page_size, head_dim]   keys are stored rotated
     block_table   [slots + 1, max_pages_per_seq] int32                logical page -> page
 
 Pages hold `page_size` (64) consecutive positions of one sequence; a sequence holds only the
 pages it has reached, so memory follows the tokens held, not slots x longest length. A group
-with a window gives pages back once no later token can read them. Fixed-size per-sequence state
+with a window gives pages back once no later token can read them (the pages of the first
+`keep_first` positions, where a request names some, are never among them). Fixed-size per-sequence state
 (for mixers that carry a recurrent state) lives beside it as [units, slots + 1, *shape] and is
 zeroed when a slot is taken; this architecture asks for none. A unit may hold several requests of
 either kind, told apart by name (a layer with two mixers). Slot `n_slots` and page
@@ -35,15 +36,23 @@ PAGE_SIZE = 64
 @dataclass(frozen=True)
 class KVRequest:
     """A mixer asks for keys and values of every earlier position (window 0) or of the last
-    `window` positions. `name` tells several such requests of one unit apart."""
+    `window` positions; with `keep_first` the first that many positions stay readable behind the window too.
+    `v_head_dim` is the size of a value head where it differs from a key head's (None: the same). `name`
+    tells several such requests of one unit apart."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     name: str = "kv"
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
-    def geometry(self) -> Tuple[int, int, int]:
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    def geometry(self) -> Tuple[int, int, int, int, int]:
         """What decides which group's storage serves the request."""
-        return (self.n_kv_heads, self.head_dim, self.window)
+        return (self.n_kv_heads, self.head_dim, self.window, self.value_dim, self.keep_first if self.window else 0)
 
 
 @dataclass(frozen=True)
@@ -59,10 +68,11 @@ class StateRequest:
 class KVUnit:
     """What an attention kernel needs of one unit."""
     k: torch.Tensor              # [pages + 1, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor              # [pages + 1, kv_heads, page_size, value head size]
     block_table: torch.Tensor    # [slots + 1, max_pages_per_seq] int32
     page_size: int
     window: int
+    keep_first: int = 0
 
 
 class CacheUnit:
@@ -87,14 +97,14 @@ class _KVGroup:
                  dtype: torch.dtype, device):
         self.req = req
         self.units = units
-        self.table = PageTableHost(n_pages, PAGE_SIZE, max_pages_per_seq, req.window)
-        shape = (len(units), n_pages + 1, req.n_kv_heads, PAGE_SIZE, req.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.table = PageTableHost(n_pages, PAGE_SIZE, max_pages_per_seq, req.window, req.keep_first)
+        shape = (len(units), n_pages + 1, req.n_kv_heads, PAGE_SIZE)
+        self.k = torch.zeros(shape + (req.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (req.value_dim,), dtype=dtype, device=device)
         self.block_table = torch.full((n_slots + 1, max_pages_per_seq), n_pages, dtype=torch.int32, device=device)
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class Cache:
@@ -118,9 +128,9 @@ class Cache:
         self.seq_lens = torch.zeros(n_slots + 1, dtype=torch.int32, device=device)
 
         # groups by geometry (kv heads, head size, window); a member is (unit, request name)
-        self._groups: Dict[Tuple[int, int, int], _KVGroup] = {}
-        by_geometry: Dict[Tuple[int, int, int], List[Tuple[int, str]]] = {}
-        first_request: Dict[Tuple[int, int, int], KVRequest] = {}
+        self._groups: Dict[tuple, _KVGroup] = {}
+        by_geometry: Dict[tuple, List[Tuple[int, str]]] = {}
+        first_request: Dict[tuple, KVRequest] = {}
         state_specs: Dict[Tuple[str, Tuple[int, ...], torch.dtype], List[int]] = {}
         for u, reqs in enumerate(unit_requests):
             names = set()
@@ -150,7 +160,7 @@ class Cache:
                 if isinstance(r, KVRequest):
                     g = self._groups[r.geometry()]
                     i = g.units.index((u, r.name))
-                    kvs[r.name] = KVUnit(g.k[i], g.v[i], g.block_table, PAGE_SIZE, r.window)
+                    kvs[r.name] = KVUnit(g.k[i], g.v[i], g.block_table, PAGE_SIZE, r.window, r.keep_first if r.window else 0)
                 else:
                     units, store = self._state[(r.name, tuple(r.shape), r.dtype)]
                     state[r.name] = store[units.index(u)]

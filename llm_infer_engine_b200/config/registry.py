@@ -39,10 +39,15 @@ def known_architectures():
 
 
 def architecture_of(config_json: dict) -> Architecture:
+    """The model class is named by `architectures` (a list, its first entry counts) or, in configurations that
+    name exactly one, by `architecture` (a string)."""
     archs = config_json.get("architectures")
+    single = config_json.get("architecture")
+    if archs is None and isinstance(single, str) and single:
+        archs = [single]
     if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names; "
-                          f"known architectures: {known_architectures()}")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' a "
+                          f"name); known architectures: {known_architectures()}")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"config.json: unknown architecture {name!r}; known architectures: "

@@ -8,9 +8,15 @@
 // h reading key/value head h / (Hq / Hkv).
 //
 // A token at absolute position p of its sequence sees keys lo..p of that sequence's slot,
-// lo = max(0, p - window + 1) when window > 0, else 0. Keys of this very step were written to
-// the cache by the rotary kernel before this kernel runs, so prefill at any start position,
-// decode, and mixtures need no separate code.
+// lo = max(0, p - window + 1) when window > 0, else 0, and besides them the first `keep_first` keys of the
+// sequence (keys 0..keep_first-1 stay visible when the window has moved past them). Keys of this very step were
+// written to the cache before this kernel runs, so prefill at any start position, decode, and mixtures need
+// no separate code.
+//
+// Options beyond the reference's math, each off by default: a value head size `hdv` that differs from the
+// query/key head size; `sink`: the softmax denominator gets one more term exp(0), a key whose score is 0 and
+// whose value is nothing (p_j = exp(s_j) / (1 + sum exp(s_j))); `gate`: the output row is multiplied element
+// by element with sigmoid(gate[t * gate_ld + ...]).
 #include "common.cuh"
 #include <math.h>
 
@@ -19,12 +25,13 @@ namespace llmie {
 constexpr int kAttnWarps = 4;
 constexpr int kMaxHeadDim = 256;
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        T* __restrict__ out, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
-                       int page_size, int n_items, int n_q, int n_kv, int hd, float scale, int window) {
+                       int page_size, int n_items, int n_q, int n_kv, int hd, int hdv, float scale, int window,
+                       int keep_first, int sink, const T* __restrict__ gate, int gate_ld) {
   extern __shared__ float q_smem[];  // [kAttnWarps][hd]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * kAttnWarps + warp;
@@ -35,6 +42,7 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
   const int slot = seq_slot[tok_seq[t]];
   const int* pages = block_table + (size_t)slot * max_pages;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int kept = keep_first < lo ? keep_first : lo;     // keys [0, kept) are seen besides [lo, pos]
 
   float* qs = q_smem + warp * hd;
   const T* qrow = q + ((size_t)t * n_q + h) * hd;
@@ -47,49 +55,70 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
   for (int i = 0; i < kAcc; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
 
-  for (int base = lo; base <= pos; base += 32) {
-    const int j = base + lane;
-    const bool valid = j <= pos;
-    size_t row = 0;
-    float s = -INFINITY;
-    if (valid) {
-      const int page = pages[j / page_size];
-      row = (((size_t)page * n_kv + hk) * page_size + (j % page_size)) * hd;
-      const T* kr = k_cache + row;
-      float dot = 0.f;
-      for (int d0 = 0; d0 < hd; d0 += 8) {
-        float kv[8];
-        load8(kr + d0, kv);
+  for (int seg = 0; seg < 2; ++seg) {
+    const int first = seg == 0 ? 0 : lo;
+    const int last = seg == 0 ? kept - 1 : pos;          // inclusive
+    for (int base = first; base <= last; base += 32) {
+      const int j = base + lane;
+      const bool valid = j <= last;
+      int page_row = 0;                                   // (page * n_kv + hk) * page_size + offset in the page
+      float s = -INFINITY;
+      if (valid) {
+        const int page = pages[j / page_size];
+        page_row = (page * n_kv + hk) * page_size + (j % page_size);
+        const T* kr = k_cache + (size_t)page_row * hd;
+        float dot = 0.f;
+        if (VEC) {
+          for (int d0 = 0; d0 < hd; d0 += 8) {
+            float kv[8];
+            load8(kr + d0, kv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d0 + e], kv[e], dot);
+            for (int e = 0; e < 8; ++e) dot = fmaf(qs[d0 + e], kv[e], dot);
+          }
+        } else {
+          for (int d0 = 0; d0 < hd; ++d0) dot = fmaf(qs[d0], to_f32(kr[d0]), dot);
+        }
+        s = dot;
       }
-      s = dot;
-    }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float p = valid ? expf(s - m_new) : 0.f;
-    const float alpha = expf(m - m_new);  // m == -inf on the first chunk gives 0
-    l = l * alpha + warp_sum(p);
+      const float m_new = fmaxf(m, warp_max(s));
+      const float p = valid ? expf(s - m_new) : 0.f;
+      const float alpha = expf(m - m_new);  // m == -inf on the first chunk gives 0
+      l = l * alpha + warp_sum(p);
 #pragma unroll
-    for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
-    m = m_new;
-    const int n_here = min(32, pos - base + 1);
-    for (int jj = 0; jj < n_here; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
-      const T* vr = v_cache + rj;
+      for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
+      m = m_new;
+      const int n_here = min(32, last - base + 1);
+      for (int jj = 0; jj < n_here; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        const int rj = __shfl_sync(0xffffffffu, page_row, jj);
+        const T* vr = v_cache + (size_t)rj * hdv;
 #pragma unroll
-      for (int i = 0; i < kAcc; ++i) {
-        const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+        for (int i = 0; i < kAcc; ++i) {
+          const int d = lane + 32 * i;
+          if (d < hdv) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+        }
       }
     }
   }
+  if (sink) {
+    // one more term whose score is 0: the running maximum becomes max(m, 0) and the denominator gains exp(0 - m')
+    const float m_new = fmaxf(m, 0.f);
+    const float alpha = expf(m - m_new);
+    l = l * alpha + expf(-m_new);
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
+  }
   const float inv_l = 1.f / l;
-  T* orow = out + ((size_t)t * n_q + h) * hd;
+  T* orow = out + ((size_t)t * n_q + h) * hdv;
+  const T* grow = gate ? gate + (size_t)t * gate_ld + (size_t)h * hdv : nullptr;
 #pragma unroll
   for (int i = 0; i < kAcc; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = from_f32<T>(acc[i] * inv_l);
+    if (d < hdv) {
+      float o = acc[i] * inv_l;
+      if (grow) o = o / (1.f + expf(-to_f32(grow[d])));
+      orow[d] = from_f32<T>(o);
+    }
   }
 }
 
@@ -97,30 +126,59 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 
 using namespace llmie;
 
-// q, out: [n_tokens, n_q * hd]; caches: [n_pages, n_kv, page_size, hd]; all of `dtype`.
-extern "C" int llmie_attention_paged(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                     const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                                     const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
-                                     int n_kv, int hd, float scale, int window, int dtype, cudaStream_t stream) {
-  if (n_tokens < 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
-  if (n_q % n_kv) return LLMIE_ERR_BAD_ARG;
-  if (hd % 16 || hd > kMaxHeadDim) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (!aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+template <typename T>
+static void attention_paged_launch(bool vec, int blocks, size_t smem, cudaStream_t stream, const void* q,
+                                   const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
+                                   const int* tok_seq, const int* seq_slot, const int* block_table, int max_pages,
+                                   int page_size, int n_items, int n_q, int n_kv, int hd, int hdv, float scale,
+                                   int window, int keep_first, int sink, const void* gate, int gate_ld) {
+  if (vec)
+    attention_paged_kernel<T, true><<<blocks, kAttnWarps * 32, smem, stream>>>(
+        (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+        page_size, n_items, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, (const T*)gate, gate_ld);
+  else
+    attention_paged_kernel<T, false><<<blocks, kAttnWarps * 32, smem, stream>>>(
+        (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+        page_size, n_items, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, (const T*)gate, gate_ld);
+}
+
+// q [n_tokens, n_q * hd]; out [n_tokens, n_q * hdv]; k_cache [n_pages, n_kv, page_size, hd]; v_cache the same with
+// hdv; gate (or null) rows of n_q * hdv elements, gate_ld apart; all of `dtype`. Any hd, hdv up to 256.
+extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                        const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                        int n_kv, int hd, int hdv, float scale, int window, int keep_first, int sink,
+                                        const void* gate, int gate_ld, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || hdv <= 0 || page_size <= 0 || max_pages <= 0)
+    return LLMIE_ERR_BAD_ARG;
+  if (n_q % n_kv || keep_first < 0 || window < 0 || (gate && gate_ld < n_q * hdv)) return LLMIE_ERR_BAD_ARG;
+  if (hd > kMaxHeadDim || hdv > kMaxHeadDim) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (dtype != LLMIE_F32 && dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
   if (n_tokens == 0) return LLMIE_OK;
   const long long n_items = (long long)n_tokens * n_q;
   if (n_items > 0x7fffffffLL) return LLMIE_ERR_UNSUPPORTED_SIZE;
   const int blocks = (int)((n_items + kAttnWarps - 1) / kAttnWarps);
   const size_t smem = (size_t)kAttnWarps * hd * sizeof(float);
+  // 16-byte loads of the keys need rows that start on 16 bytes (32 for float32, two loads of 16)
+  const bool vec = hd % 8 == 0 && aligned16(k_cache);
   if (dtype == LLMIE_F32)
-    attention_paged_kernel<float><<<blocks, kAttnWarps * 32, smem, stream>>>(
-        (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, tok_pos, tok_seq, seq_slot,
-        block_table, max_pages, page_size, (int)n_items, n_q, n_kv, hd, scale, window);
-  else if (dtype == LLMIE_BF16)
-    attention_paged_kernel<__nv_bfloat16><<<blocks, kAttnWarps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
-        tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, (int)n_items, n_q, n_kv, hd, scale, window);
+    attention_paged_launch<float>(vec, blocks, smem, stream, q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot,
+                                  block_table, max_pages, page_size, (int)n_items, n_q, n_kv, hd, hdv, scale, window,
+                                  keep_first, sink, gate, gate_ld);
   else
-    return LLMIE_ERR_DTYPE;
+    attention_paged_launch<__nv_bfloat16>(vec, blocks, smem, stream, q, k_cache, v_cache, out, tok_pos, tok_seq,
+                                          seq_slot, block_table, max_pages, page_size, (int)n_items, n_q, n_kv, hd,
+                                          hdv, scale, window, keep_first, sink, gate, gate_ld);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+// The form without options: one head size, no kept first keys, no sink, no gate.
+extern "C" int llmie_attention_paged(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                     const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                     int n_kv, int hd, float scale, int window, int dtype, cudaStream_t stream) {
+  if (hd % 16) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  return llmie_attention_paged_ex(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+                                  page_size, n_tokens, n_q, n_kv, hd, hd, scale, window, 0, 0, nullptr, 0, dtype, stream);
 }

@@ -1,0 +1,329 @@
+// Memory-bound kernels of layers whose norm sits on the OUTPUT of a branch (h += norm(f(h))), of an embedding stage
+// with learned positions, of feed-forwards with biases, and of attention layers that normalise the whole query
+// and key projections and may blend their values with those of an earlier layer.
+//
+// Everything that is summed, normalised or blended here is float32: the residual stream, the sums of squares,
+// the norm's scale, the blend. Activations between products are T (float or bfloat16), rounded once at the store.
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+static inline int row_threads(int d) {
+  int t = ((d + 31) / 32) * 32;
+  return t < 32 ? 32 : (t > 512 ? 512 : t);
+}
+
+// ------------------------------------------------------------------------------------------
+// Embedding stage: x = h[t] * scale + pos_table[tok_pos[t]];  h[t] = norm_w ? x * rsqrt(mean(x^2) + eps) * norm_w : x;
+// act[t] = h[t] rounded to A (optional). pos_table and norm_w are optional. One block per token.
+template <typename P, typename A>
+__global__ void scale_pos_norm_kernel(float* __restrict__ h, float scale, const P* __restrict__ pos_table,
+                                      int table_len, const int* __restrict__ tok_pos,
+                                      const float* __restrict__ norm_w, float eps, A* __restrict__ act, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  float* hr = h + (size_t)t * d;
+  const P* pr = nullptr;
+  if (pos_table) {
+    int p = tok_pos[t];
+    p = p < 0 ? 0 : (p >= table_len ? table_len - 1 : p);     // the host refuses longer sequences
+    pr = pos_table + (size_t)p * d;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = hr[i] * scale;
+    if (pr) x += to_f32(pr[i]);
+    row_buf[i] = x;
+    ss += x * x;
+  }
+  float rstd = 1.f;
+  if (norm_w) {
+    ss = block_sum(ss, red);
+    rstd = 1.f / sqrtf(ss / (float)d + eps);
+  }
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float y = norm_w ? row_buf[i] * rstd * norm_w[i] : row_buf[i];
+    hr[i] = y;
+    if (act) act[(size_t)t * d + i] = from_f32<A>(y);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Norm on a branch's output, then the residual add:
+//   x = y[t] (+ bias);  h[t] += x * rsqrt(mean(x^2) + eps) * w;  act[t] = h[t] rounded to A (optional)
+// One block per row.
+template <typename Y, typename A>
+__global__ void branch_norm_add_kernel(float* __restrict__ h, const Y* __restrict__ y, const float* __restrict__ bias,
+                                       const float* __restrict__ w, float eps, A* __restrict__ act, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const Y* yr = y + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = to_f32(yr[i]);
+    if (bias) x += bias[i];
+    row_buf[i] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)d + eps);
+  float* hr = h + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float s = hr[i] + row_buf[i] * rstd * w[i];
+    hr[i] = s;
+    if (act) act[(size_t)t * d + i] = from_f32<A>(s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t, j] = act(u[t, j] + bias[j]); bias optional. Activations: 0 none, 1 relu, 2 relu squared, 3 gelu (tanh
+// form), 4 silu.
+__device__ __forceinline__ float apply_act(float z, int act) {
+  switch (act) {
+    case 1: return fmaxf(z, 0.f);
+    case 2: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 3: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 4: return z / (1.f + expf(-z));
+    default: return z;
+  }
+}
+
+template <typename T, typename O>
+__global__ void bias_act_kernel(const T* __restrict__ u, const float* __restrict__ bias, O* __restrict__ out, int n,
+                                size_t total, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    float z = to_f32(u[i]);
+    if (bias) z += bias[i % n];
+    out[i] = from_f32<O>(apply_act(z, act));
+  }
+}
+
+// out = float32 -> A, element by element
+template <typename A>
+__global__ void cast_rows_kernel(const float* __restrict__ x, A* __restrict__ out, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) out[i] = from_f32<A>(x[i]);
+}
+
+// out[t, j] *= sigmoid(gate[t * ld + j])
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ gate, int ld, int n, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / n;
+    const int j = (int)(i - t * n);
+    const float g = to_f32(gate[t * ld + j]);
+    out[i] = from_f32<T>(to_f32(out[i]) / (1.f + expf(-g)));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Whole-projection query/key norm, value blending and the cache write of one attention layer.
+//   proj[t] (row stride ld) = [ q : n_q*hd | k : n_kv*hd | v : n_kv*hdv | ... ]
+//   q_out[t]  = q * rsqrt(mean over ALL n_q*hd elements of q^2 + eps) * q_w      (q_w null: q unchanged)
+//   k' likewise over all n_kv*hd elements with k_w;  v' = v_first ? (1 - lam) v + lam v_first[t] : v
+//   k_cache[page(t), hk, pos % P, :] = k'   v_cache[...] = v'   (only with write_kv)
+// lam is read from device memory (a checkpoint scalar). One block per token.
+template <typename T>
+__global__ void qk_norm_store_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, const float* __restrict__ q_w,
+                                     const float* __restrict__ k_w, float eps, const float* __restrict__ lam_ptr,
+                                     const T* __restrict__ v_first, int v_first_ld, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                     const int* __restrict__ block_table, int max_pages, int page_size, int n_q,
+                                     int n_kv, int hd, int hdv, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int nq = n_q * hd, nk = n_kv * hd, nv = n_kv * hdv;
+  const T* qs = proj + (size_t)t * ld;
+  const T* ks = qs + nq;
+  const T* vs = ks + nk;
+  float rq = 1.f, rk = 1.f;
+  if (q_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float x = to_f32(qs[i]); ss += x * x; }
+    ss = block_sum(ss, red);
+    rq = 1.f / sqrtf(ss / (float)nq + eps);
+  }
+  if (k_w && write_kv) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float x = to_f32(ks[i]); ss += x * x; }
+    ss = block_sum(ss, red);
+    rk = 1.f / sqrtf(ss / (float)nk + eps);
+  }
+  T* qo = q_out + (size_t)t * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x)
+    qo[i] = q_w ? from_f32<T>(to_f32(qs[i]) * rq * q_w[i]) : qs[i];
+  if (!write_kv) return;
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+  const int in_page = pos % page_size;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int hk = i / hd, e = i - hk * hd;
+    const size_t dst = (((size_t)page * n_kv + hk) * page_size + in_page) * hd + e;
+    k_cache[dst] = k_w ? from_f32<T>(to_f32(ks[i]) * rk * k_w[i]) : ks[i];
+  }
+  const float lam = v_first ? *lam_ptr : 0.f;
+  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int hk = i / hdv, e = i - hk * hdv;
+    const size_t dst = (((size_t)page * n_kv + hk) * page_size + in_page) * hdv + e;
+    T v = vs[i];
+    if (vf) v = from_f32<T>((1.f - lam) * to_f32(v) + lam * to_f32(vf[i]));
+    v_cache[dst] = v;
+  }
+}
+
+template <typename A> struct DT { };
+template <> struct DT<float> { static constexpr int code = LLMIE_F32; };
+template <> struct DT<__nv_bfloat16> { static constexpr int code = LLMIE_BF16; };
+
+static inline int flat_blocks(size_t total) {
+  size_t b = (total + 255) / 256;
+  return (int)(b > 148 * 16 ? 148 * 16 : (b == 0 ? 1 : b));
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+// h float32 [T, d] in place; pos_table [table_len, d] of pos_dtype or null; norm_w float32 [d] or null;
+// act [T, d] of act_dtype or null.
+extern "C" int llmie_scale_pos_norm(float* h, float scale, const void* pos_table, int pos_dtype, int table_len,
+                                    const int* tok_pos, const float* norm_w, float eps, void* act, int act_dtype,
+                                    int n_tokens, int d, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || (pos_table && (table_len <= 0 || !tok_pos))) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const dim3 grid(n_tokens), block(row_threads(d));
+#define LLMIE_SPN(P, A)                                                                                          \
+  launch_k(scale_pos_norm_kernel<P, A>, grid, block, smem, stream, h, scale, (const P*)pos_table, table_len,     \
+           tok_pos, norm_w, eps, (A*)act, d)
+  const bool pos_bf16 = pos_table && pos_dtype == LLMIE_BF16;
+  if (pos_table && pos_dtype != LLMIE_BF16 && pos_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  if (act && act_dtype != LLMIE_BF16 && act_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  const bool act_bf16 = act && act_dtype == LLMIE_BF16;
+  if (pos_bf16 && act_bf16) LLMIE_SPN(__nv_bfloat16, __nv_bfloat16);
+  else if (pos_bf16) LLMIE_SPN(__nv_bfloat16, float);
+  else if (act_bf16) LLMIE_SPN(float, __nv_bfloat16);
+  else LLMIE_SPN(float, float);
+#undef LLMIE_SPN
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// h float32 [T, d] += norm(y (+ bias)) * w; y [T, d] of y_dtype; bias float32 [d] or null; act of act_dtype or null.
+extern "C" int llmie_branch_norm_add(float* h, const void* y, int y_dtype, const float* bias, const float* w, float eps,
+                                     void* act, int act_dtype, int n_tokens, int d, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || !w || !y) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (y_dtype != LLMIE_BF16 && y_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  if (act && act_dtype != LLMIE_BF16 && act_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  const dim3 grid(n_tokens), block(row_threads(d));
+#define LLMIE_BNA(Y, A)                                                                                          \
+  launch_k(branch_norm_add_kernel<Y, A>, grid, block, smem, stream, h, (const Y*)y, bias, w, eps, (A*)act, d)
+  const bool y_bf16 = y_dtype == LLMIE_BF16, act_bf16 = act && act_dtype == LLMIE_BF16;
+  if (y_bf16 && act_bf16) LLMIE_BNA(__nv_bfloat16, __nv_bfloat16);
+  else if (y_bf16) LLMIE_BNA(__nv_bfloat16, float);
+  else if (act_bf16) LLMIE_BNA(float, __nv_bfloat16);
+  else LLMIE_BNA(float, float);
+#undef LLMIE_BNA
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// out[T, n] (out_dtype) = act(u[T, n] (u_dtype) + bias[n]); bias float32 or null.
+extern "C" int llmie_bias_act(const void* u, int u_dtype, const float* bias, void* out, int out_dtype, int n_tokens,
+                              int n, int act, cudaStream_t stream) {
+  if (n_tokens < 0 || n <= 0 || act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * n;
+  const dim3 grid(flat_blocks(total)), block(256);
+#define LLMIE_BA(T, O) launch_k(bias_act_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n, total, act)
+  if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_F32) LLMIE_BA(float, float);
+  else if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_BF16) LLMIE_BA(float, __nv_bfloat16);
+  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_BF16) LLMIE_BA(__nv_bfloat16, __nv_bfloat16);
+  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_F32) LLMIE_BA(__nv_bfloat16, float);
+  else return LLMIE_ERR_DTYPE;
+#undef LLMIE_BA
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_cast_rows(const float* x, void* out, int out_dtype, long long total, cudaStream_t stream) {
+  if (total < 0) return LLMIE_ERR_BAD_ARG;
+  if (total == 0) return LLMIE_OK;
+  const dim3 grid(flat_blocks((size_t)total)), block(256);
+  if (out_dtype == LLMIE_BF16) launch_k(cast_rows_kernel<__nv_bfloat16>, grid, block, 0, stream, x, (__nv_bfloat16*)out, (size_t)total);
+  else if (out_dtype == LLMIE_F32) launch_k(cast_rows_kernel<float>, grid, block, 0, stream, x, (float*)out, (size_t)total);
+  else return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// out[T, n] *= sigmoid(gate[t * ld + j]); both of `dtype`.
+extern "C" int llmie_sigmoid_gate(void* out, const void* gate, int ld, int n_tokens, int n, int dtype,
+                                  cudaStream_t stream) {
+  if (n_tokens < 0 || n <= 0 || ld < n) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * n;
+  const dim3 grid(flat_blocks(total)), block(256);
+  if (dtype == LLMIE_F32) launch_k(sigmoid_gate_kernel<float>, grid, block, 0, stream, (float*)out, (const float*)gate, ld, n, total);
+  else if (dtype == LLMIE_BF16) launch_k(sigmoid_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ld, n, total);
+  else return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// proj [T, ld]; q_out [T, n_q hd]; k_cache [pages, n_kv, page_size, hd]; v_cache [pages, n_kv, page_size, hdv]; all
+// of `dtype`. q_w, k_w float32 or null; lam_ptr float32 scalar on the device (needed with v_first); v_first rows of
+// n_kv*hdv elements, v_first_ld apart, or null.
+extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* k_cache, void* v_cache, const float* q_w,
+                                   const float* k_w, float eps, const float* lam_ptr, const void* v_first,
+                                   int v_first_ld, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                   const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                   int n_kv, int hd, int hdv, int write_kv, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || hdv <= 0 || page_size <= 0 || max_pages <= 0)
+    return LLMIE_ERR_BAD_ARG;
+  if (ld < n_q * hd + n_kv * hd + n_kv * hdv) return LLMIE_ERR_BAD_ARG;
+  if (v_first && (!lam_ptr || v_first_ld < n_kv * hdv)) return LLMIE_ERR_BAD_ARG;
+  if (write_kv && (!k_cache || !v_cache)) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const dim3 grid(n_tokens), block(row_threads(n_q * hd));
+  if (dtype == LLMIE_F32)
+    launch_k(qk_norm_store_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, (float*)q_out,
+             (float*)k_cache, (float*)v_cache, q_w, k_w, eps, lam_ptr, (const float*)v_first, v_first_ld, tok_pos,
+             tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, write_kv);
+  else if (dtype == LLMIE_BF16)
+    launch_k(qk_norm_store_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld,
+             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_w, k_w, eps, lam_ptr,
+             (const __nv_bfloat16*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size,
+             n_q, n_kv, hd, hdv, write_kv);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

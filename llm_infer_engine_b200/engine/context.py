@@ -12,7 +12,7 @@ host-side bounds needed to size launches, and the attention service that picks a
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional
 
 import torch
@@ -41,6 +41,10 @@ class StepContext:
     kernels: Optional[object] = None     # the engine's kernel choices (KernelPlan)
     all_rows: bool = False               # logit_rows is 0..n_tokens-1: every row's logits are wanted
     entry: int = 0                       # which entry of the run order is running (set by the model, for traces)
+    # What one layer leaves for later layers of the SAME step, by name: the values of the first layer that later
+    # layers blend with their own, or the residual stream already rounded for the next product. Emptied with
+    # the step; nothing in here outlives it.
+    carry: dict = field(default_factory=dict)
 
     def attention_with_rope(self, qkv, table, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions,
                             write_kv: bool) -> bool:
@@ -51,11 +55,18 @@ class StepContext:
         return plan is not None and plan.attention_with_rope(self, qkv, table, kv, out, n_q, n_kv, head_dim, options,
                                                              write_kv)
 
-    def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions) -> None:
+    def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions,
+                  gate: Optional[torch.Tensor] = None) -> None:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own
-        sequence up to its own position (and no further back than `options.window`, if set)."""
+        sequence up to its own position (and no further back than `options.window`, if set, except the first
+        `options.keep_first` keys). The value head size is the cache's. With `gate` ([T, n_q * value head size],
+        possibly a column slice) the output is multiplied by sigmoid(gate), inside the attention kernel where it
+        can do that, else by a kernel of its own."""
         plan = self.kernels
         if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, options):
+            if gate is not None:
+                ops.sigmoid_gate(out, gate)
             return
         ops.attention_paged(q, kv.k, kv.v, out, self.tok_pos, self.tok_seq, self.seq_slot, kv.block_table,
-                            kv.page_size, n_q, n_kv, head_dim, options.scale, options.window)
+                            kv.page_size, n_q, n_kv, head_dim, options.scale, options.window, options.keep_first,
+                            options.sink, gate)

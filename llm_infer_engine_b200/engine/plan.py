@@ -56,6 +56,8 @@ class KernelPlan:
         """Returns True when a specialised kernel ran. Every kernel below takes the options there are
         today (scale, window); a new option is checked here, kernel by kernel."""
         scale, window = options.scale, options.window
+        if not options.plain or kv.v.shape[-1] != head_dim:
+            return False       # kept first keys, a sink or a value head size of its own: the plain kernel knows them
         if ctx.decode and self.decode_attention != "split" \
                 and ops.attention_decode_mma_supported(head_dim, q.dtype, kv.page_size):
             # bfloat16, head size 64 or 128: a warp per page on the tensor cores

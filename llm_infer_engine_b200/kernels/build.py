@@ -29,6 +29,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
 # family -> (source file, extra nvcc flags, extra link flags)
 FAMILIES: Dict[str, tuple] = {
     "elementwise": ("elementwise.cu", [], []),
+    "branch_elementwise": ("branch_elementwise.cu", [], []),
     "attention_simt": ("attention_simt.cu", [], []),
     "attention_decode": ("attention_decode.cu", [], []),
     "attention_decode_mma": ("attention_decode_mma.cu", [], []),

@@ -252,26 +252,177 @@ def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, 
 
 
 def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
-                    n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
+                    n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0, keep_first: int = 0,
+                    sink: bool = False, gate: Optional[torch.Tensor] = None):
     """Plain attention over the paged cache, one warp per (token, query head).
-    q, out [T, n_q hd]; caches [n_pages, n_kv, page_size, hd]; window 0 = all earlier keys."""
+    q [T, n_q hd]; out [T, n_q hdv]; k_cache [n_pages, n_kv, page_size, hd]; v_cache the same with hdv (the value
+    head size, read from its shape). window 0 = all earlier keys; the first `keep_first` keys of a sequence stay
+    visible behind the window; `sink` adds a key of score 0 without a value to the softmax; `gate` (rows of
+    n_q hdv elements, possibly a column slice of a wider tensor) multiplies the output by its sigmoid."""
     T = q.shape[0]
+    hdv = v_cache.shape[-1]
     _need(q, "q", None, (T, n_q * head_dim))
-    _need(out, "out", q.dtype, (T, n_q * head_dim))
+    _need(out, "out", q.dtype, (T, n_q * hdv))
     _need(k_cache, "k_cache", q.dtype, (None, n_kv, page_size, head_dim))
-    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
+    _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], n_kv, page_size, hdv))
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
         _need(t, name, torch.int32)
-    if head_dim % 16 or head_dim > 256:
-        raise KernelError(f"attention_paged: head_dim {head_dim} must be a multiple of 16 and at most 256")
-    _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * q.element_size(),
-          4.0 * n_q * head_dim * STEP_HINT["pairs"])
-    f = _fn("attention_simt", "llmie_attention_paged",
-            [_c_void_p] * 8 + [_c_int] * 6 + [_c_float, _c_int, _c_int, _c_void_p])
+    if head_dim > 256 or hdv > 256:
+        raise KernelError(f"attention_paged: head sizes {head_dim} / {hdv} must be at most 256")
+    gate_ld = 0
+    if gate is not None:
+        gate_ld = _row_slice(gate, "gate", q.dtype, T, n_q * hdv)
+    _work(2 * _nbytes(q) + 1.0 * STEP_HINT["kv_total"] * n_kv * (head_dim + hdv) * q.element_size(),
+          2.0 * n_q * (head_dim + hdv) * STEP_HINT["pairs"])
+    f = _fn("attention_simt", "llmie_attention_paged_ex",
+            [_c_void_p] * 8 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tok_pos.data_ptr(),
              tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T,
-             n_q, n_kv, head_dim, float(scale), int(window), _dt(q, "q"), _stream()), "attention_paged")
+             n_q, n_kv, head_dim, hdv, float(scale), int(window), int(keep_first), 1 if sink else 0, _ptr(gate),
+             gate_ld, _dt(q, "q"), _stream()), "attention_paged")
     return out
+
+
+def _row_slice(t: torch.Tensor, what: str, dtype, rows: int, cols: int) -> int:
+    """Checks a [rows, cols] tensor that may be a column slice of a wider contiguous one; returns its row stride."""
+    if not t.is_cuda:
+        raise KernelError(f"{what}: must be a CUDA tensor")
+    if t.dtype is not dtype:
+        raise KernelError(f"{what}: dtype {t.dtype}, expected {dtype}")
+    if t.dim() != 2 or t.shape[0] != rows or t.shape[1] != cols:
+        raise KernelError(f"{what}: shape {tuple(t.shape)}, expected {(rows, cols)}")
+    if t.stride(1) != 1 or (rows > 1 and t.stride(0) < cols):
+        raise KernelError(f"{what}: rows must be contiguous runs of {cols} elements")
+    return t.stride(0) if rows > 1 else max(t.stride(0), cols)
+
+
+ACT_NONE, ACT_RELU, ACT_RELU2, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+ACTIVATIONS = {"none": ACT_NONE, "relu": ACT_RELU, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+
+
+def scale_pos_norm(h, scale: float, pos_table, tok_pos, norm_w, eps: float, act=None):
+    """h (float32 [T, d], in place) = norm(h * scale + pos_table[tok_pos]); pos_table [P, d] (float32 or bfloat16)
+    and norm_w (float32 [d]) are optional; act (optional, [T, d]) receives h rounded to its dtype."""
+    T, d = h.shape
+    _need(h, "h", torch.float32)
+    if pos_table is not None:
+        _need(pos_table, "pos_table", None, (None, d))
+        _need(tok_pos, "tok_pos", torch.int32)
+        if tok_pos.shape[0] < T:
+            raise KernelError("scale_pos_norm: tok_pos shorter than the token count")
+    if norm_w is not None:
+        _need(norm_w, "norm_w", torch.float32, (d,))
+    if act is not None:
+        _need(act, "act", None, (T, d))
+    _work(2 * _nbytes(h) + _nbytes(act) + (T * d * pos_table.element_size() if pos_table is not None else 0))
+    f = _fn("branch_elementwise", "llmie_scale_pos_norm",
+            [_c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int,
+             _c_int, _c_void_p])
+    _check(f(h.data_ptr(), float(scale), _ptr(pos_table), _dt(pos_table, "pos_table") if pos_table is not None else 0,
+             pos_table.shape[0] if pos_table is not None else 0, _ptr(tok_pos) if pos_table is not None else None,
+             _ptr(norm_w), float(eps), _ptr(act), _dt(act, "act") if act is not None else 0, T, d, _stream()),
+           "scale_pos_norm")
+    return h
+
+
+def branch_norm_add(h, y, bias, weight, eps: float, act=None):
+    """h (float32 [T, d]) += rmsnorm(y + bias) * weight: the norm sits on a branch's output. y [T, d] float32 or
+    bfloat16; bias float32 [d] or None; act (optional [T, d]) receives the new h rounded to its dtype."""
+    T, d = h.shape
+    _need(h, "h", torch.float32)
+    _need(y, "y", None, (T, d))
+    _need(weight, "weight", torch.float32, (d,))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (d,))
+    if act is not None:
+        _need(act, "act", None, (T, d))
+    _work(2 * _nbytes(h) + _nbytes(y, act))
+    f = _fn("branch_elementwise", "llmie_branch_norm_add",
+            [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), y.data_ptr(), _dt(y, "y"), _ptr(bias), weight.data_ptr(), float(eps), _ptr(act),
+             _dt(act, "act") if act is not None else 0, T, d, _stream()), "branch_norm_add")
+    return h
+
+
+def bias_act(u, bias, out, act: int):
+    """out[T, n] = act(u[T, n] + bias[n]); bias float32 or None; act one of the ACT_* codes."""
+    T, n = u.shape
+    _need(u, "u")
+    _need(out, "out", None, (T, n))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    _work(_nbytes(u, out))
+    f = _fn("branch_elementwise", "llmie_bias_act",
+            [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(u.data_ptr(), _dt(u, "u"), _ptr(bias), out.data_ptr(), _dt(out, "out"), T, n, int(act), _stream()),
+           "bias_act")
+    return out
+
+
+def cast_rows(x, out):
+    """out = x (float32) rounded to out's dtype."""
+    _need(x, "x", torch.float32)
+    _need(out, "out", None, tuple(x.shape))
+    _work(_nbytes(x, out))
+    f = _fn("branch_elementwise", "llmie_cast_rows", [_c_void_p, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p])
+    _check(f(x.data_ptr(), out.data_ptr(), _dt(out, "out"), x.numel(), _stream()), "cast_rows")
+    return out
+
+
+def sigmoid_gate(out, gate):
+    """out[T, n] *= sigmoid(gate[T, n]); gate may be a column slice of a wider tensor."""
+    T, n = out.shape
+    _need(out, "out")
+    ld = _row_slice(gate, "gate", out.dtype, T, n)
+    _work(2 * _nbytes(out) + T * n * out.element_size())
+    f = _fn("branch_elementwise", "llmie_sigmoid_gate", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(out.data_ptr(), gate.data_ptr(), ld, T, n, _dt(out, "out"), _stream()), "sigmoid_gate")
+    return out
+
+
+def qk_norm_store(proj, q_out, k_cache, v_cache, q_w, k_w, eps: float, tok_pos, tok_seq, seq_slot, block_table,
+                  page_size: int, n_q: int, n_kv: int, head_dim: int, v_head_dim: int, write_kv: bool = True,
+                  lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None):
+    """RMS norm over the WHOLE query projection and over the whole key projection (not per head), value blending,
+    and the cache write. proj [T, >= n_q hd + n_kv hd + n_kv hdv] holds [q | k | v | ...] per row; q_out [T, n_q hd];
+    q_w / k_w float32 weights of the norms (None: that projection is copied as it is); with `v_first` (rows of
+    n_kv hdv values, possibly a column slice) the stored values are (1 - lam) v + lam v_first, lam a float32 scalar
+    on the device."""
+    T, ld = proj.shape
+    nq, nk, nv = n_q * head_dim, n_kv * head_dim, n_kv * v_head_dim
+    _need(proj, "proj")
+    if ld < nq + nk + nv:
+        raise KernelError(f"qk_norm_store: rows of {ld} elements cannot hold q, k and v ({nq} + {nk} + {nv})")
+    _need(q_out, "q_out", proj.dtype, (T, nq))
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if tok_pos.shape[0] < T or tok_seq.shape[0] < T:
+        raise KernelError("qk_norm_store: tok_pos / tok_seq shorter than the token count")
+    if q_w is not None:
+        _need(q_w, "q_w", torch.float32, (nq,))
+    if k_w is not None:
+        _need(k_w, "k_w", torch.float32, (nk,))
+    if write_kv:
+        _need(k_cache, "k_cache", proj.dtype, (None, n_kv, page_size, head_dim))
+        _need(v_cache, "v_cache", proj.dtype, (k_cache.shape[0], n_kv, page_size, v_head_dim))
+    vf_ld = 0
+    if v_first is not None:
+        vf_ld = _row_slice(v_first, "v_first", proj.dtype, T, nv)
+        if lam is None:
+            raise KernelError("qk_norm_store: v_first needs lam")
+        _need(lam, "lam", torch.float32)
+        if lam.numel() != 1:
+            raise KernelError("qk_norm_store: lam must hold one number")
+    _work((T * (nq + nk + nv) + T * nq + (T * (nk + nv) if write_kv else 0)) * proj.element_size())
+    f = _fn("branch_elementwise", "llmie_qk_norm_store",
+            [_c_void_p, _c_int] + [_c_void_p] * 5 + [_c_float, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 4 +
+            [_c_int] * 9 + [_c_void_p])
+    _check(f(proj.data_ptr(), ld, q_out.data_ptr(), _ptr(k_cache) if write_kv else None,
+             _ptr(v_cache) if write_kv else None, _ptr(q_w), _ptr(k_w), float(eps), _ptr(lam) if v_first is not None else None,
+             _ptr(v_first), vf_ld, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], page_size, T, n_q, n_kv, head_dim, v_head_dim, 1 if write_kv else 0,
+             _dt(proj, "proj"), _stream()), "qk_norm_store")
+    return q_out
 
 
 def attention_decode_supported(head_dim: int, dtype: torch.dtype) -> bool:

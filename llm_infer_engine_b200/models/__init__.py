@@ -1,4 +1,4 @@
-from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import llama, zemivik  # noqa: F401  (register LlamaForCausalLM and Zemivik)
 from .decoder import DecoderModel
 
 __all__ = ["DecoderModel"]

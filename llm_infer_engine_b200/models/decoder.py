@@ -57,20 +57,29 @@ class DecoderModel:
         for i, (layer, block) in enumerate(zip(self.spec.layers, self.blocks)):
             prefix = self.spec.layer_prefix.format(i=i)
             for role, part in block.parts().items():
-                out.append((prefix + layer.names[role] + ".", part))
-        out.append((self.spec.final_norm_name + ".", self.final_norm))
+                out.append((prefix + layer.names[role], part))
+        out.append((self.spec.final_norm_name, self.final_norm))
         if self.after_embedding is not None:
-            out.append((self.spec.after_embedding_name + ".", self.after_embedding))
+            out.append((self.spec.after_embedding_name, self.after_embedding))
         if self.after_head is not None:
-            out.append((self.spec.after_head_name + ".", self.after_head))
+            out.append((self.spec.after_head_name, self.after_head))
         return out
+
+    @staticmethod
+    def _full_name(part_name: str, local: str) -> str:
+        """A part's tensor in the checkpoint: `<part>.<local>`; a part whose tensor has the empty local name is
+        stored under the part's own name, and a part without a name of its own (the empty string) stores its
+        tensors under their local names."""
+        if not local:
+            return part_name
+        return f"{part_name}.{local}" if part_name else local
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Every checkpoint tensor this model reads, by full name."""
         specs = {self.spec.embedding_name: ParamSpec((self.vocab_size, self.hidden_size))}
         for prefix, part in self._named_parts():
             for local, ps in part.param_specs().items():
-                specs[prefix + local] = ps
+                specs[self._full_name(prefix, local)] = ps
         if not self.spec.tie_head:
             specs[self.spec.head_name] = ParamSpec((self.vocab_size, self.hidden_size))
         return specs
@@ -79,7 +88,8 @@ class DecoderModel:
         """tensors: full name -> device tensor, for exactly the names of param_specs()."""
         self.embedding = tensors[self.spec.embedding_name].contiguous()
         for prefix, part in self._named_parts():
-            part.load({local: tensors[prefix + local] for local in part.param_specs()})
+            part.load({local: tensors[self._full_name(prefix, local)] for local, ps in part.param_specs().items()
+                       if not ps.optional or self._full_name(prefix, local) in tensors})
         self.head = Linear(self.embedding if self.spec.tie_head else tensors[self.spec.head_name])
 
     def weight_bytes_per_step(self) -> int:
@@ -103,8 +113,12 @@ class DecoderModel:
         for pos, call in enumerate(self.spec.schedule):
             unit = cache.unit(self.unit_of_entry[pos])
             ctx.entry = pos
-            h, pending = self.blocks[call.layer].forward(h, pending, ctx, unit, call.cache_of is None)
+            block = self.blocks[call.layer]
+            h, pending = block.forward(h, pending, ctx, unit, call.cache_of is None)
+            if not getattr(block, "leaves_rounded_stream", False):
+                ctx.carry.pop("h_act", None)      # a rounded copy of the stream from before this block is stale
         trace.pop()
+        ctx.carry.clear()
         trace.push("Output")
         logits = None
         if pending is None and ctx.all_rows and self.head.weight.dtype == torch.bfloat16 \

@@ -39,10 +39,12 @@ class Runtime:
 class ParamSpec:
     """A checkpoint tensor of a part. `role`: "matrix" (a GEMM operand), "vector" (norm weights,
     biases) or "table" (integers). `init` is how the random-weights mode fills it:
-    ("normal",) uses the caller's std, ("ones",), ("zeros",) or ("uniform", lo, hi)."""
+    ("normal",) uses the caller's std, ("ones",), ("zeros",) or ("uniform", lo, hi). The random-weights mode
+    writes optional tensors too."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: Tuple = ("normal",)
+    optional: bool = False        # a tensor that a checkpoint may hold or not; `load` gets it only when it is there
 
 
 @dataclass(frozen=True)
@@ -53,6 +55,13 @@ class AttentionOptions:
     knows it (the plain kernel first), so the call sites of the existing options do not change."""
     scale: float
     window: int = 0              # 0 = every earlier key; n = the last n keys, the token's own included
+    keep_first: int = 0          # with a window: the first n keys of the sequence stay visible behind it
+    sink: bool = False           # one more term exp(0) in the softmax's denominator (a key of score 0, no value)
+
+    @property
+    def plain(self) -> bool:
+        """Only the options every attention kernel knows (scale, window)."""
+        return self.keep_first == 0 and not self.sink
 
 
 class Part:
@@ -76,6 +85,12 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """h (float32 [T, d]) += delta in place when rows is None; returns norm(h) in the
         activation dtype. With `rows`, only those rows are produced and h is untouched."""
+        raise NotImplementedError
+
+    def add_normed(self, h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   act: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """For blocks whose norm sits on a branch's OUTPUT: h (float32 [T, d]) += norm(y + bias) in place. `act`,
+        if given, receives the new h rounded to its dtype (the next product's input)."""
         raise NotImplementedError
 
     def defer(self, h: torch.Tensor) -> Optional["DeferredNorm"]:

@@ -3,7 +3,9 @@
 branch output travels to the next norm as `pending`."""
 from __future__ import annotations
 
-from ..kernels import trace
+import torch
+
+from ..kernels import ops, trace
 from .base import Block, call_branch, register_block
 
 
@@ -38,3 +40,71 @@ class PreNormBlock(Block):
 
 
 register_block("pre_norm", PreNormBlock)
+
+
+class BranchNormBlock(Block):
+    """h += norm(mixer(h)); h += norm(feed_forward(h)): the branches read the residual stream itself and the norm
+    sits on each branch's OUTPUT. The sum stays float32; a bfloat16 engine's products read the stream rounded to
+    bfloat16, and that rounded copy is written by the same kernel that adds the branch (it travels to the next
+    layer in `ctx.carry["h_act"]`). A feed-forward that declares `down_bias` has it added inside the norm's
+    kernel."""
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+    leaves_rounded_stream = True
+
+    def _rounded(self, h, ctx):
+        """The stream as the products read it: itself in a float32 engine, else its bfloat16 copy."""
+        if self.runtime.dtype == torch.float32:
+            return h
+        act = ctx.carry.pop("h_act", None)
+        if act is None:
+            act = ops.cast_rows(h, torch.empty(h.shape, dtype=self.runtime.dtype, device=h.device))
+        return act
+
+    def _new_rounded(self, h):
+        return None if self.runtime.dtype == torch.float32 else torch.empty(h.shape, dtype=self.runtime.dtype,
+                                                                            device=h.device)
+
+    def _mixer_branch(self, h, pending, ctx, unit, owns_cache):
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.carry.pop("h_act", None)
+        x = self._rounded(h, ctx)
+        y = call_branch(self.mixer, x, ctx, unit, owns_cache)
+        act = self._new_rounded(h)
+        self.mixer_norm.add_normed(h, y, None, act)
+        return act
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        tracing = trace.active()
+        if tracing:
+            trace.push(f"Attn_{ctx.entry}")
+        act = self._mixer_branch(h, pending, ctx, unit, owns_cache)
+        if tracing:
+            trace.pop()
+            trace.push(f"FFN_{ctx.entry}")
+        ff = self.feed_forward
+        deferred = getattr(ff, "down_bias", None)
+        x = h if act is None else act
+        y = ff.forward(x, ctx, defer_bias=True) if deferred is not None else call_branch(ff, x, ctx)
+        act = self._new_rounded(h)
+        self.feed_forward_norm.add_normed(h, y, deferred, act)
+        if act is not None:
+            ctx.carry["h_act"] = act
+        if tracing:
+            trace.pop()
+        return h, None
+
+
+class BranchNormMixerBlock(BranchNormBlock):
+    """The same arrangement for a layer without a feed-forward: h += norm(mixer(h))."""
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        act = self._mixer_branch(h, pending, ctx, unit, owns_cache)
+        if act is not None:
+            ctx.carry["h_act"] = act
+        return h, None
+
+
+register_block("branch_norm", BranchNormBlock)
+register_block("branch_norm_mixer", BranchNormMixerBlock)

@@ -1,0 +1,135 @@
+"""Gated grouped-query attention without rotation, over a window that keeps the first tokens.
+
+With h the layer's input [T, d], H query heads of size D, G key/value heads (query head i reads key/value head
+i // (H / G)), and value heads of size Dv:
+
+    q = h Wq^T, k = h Wk^T, v = h Wv^T, g = h Wg^T                      one product over row-concatenated weights
+    q <- q / sqrt(mean(q^2) + eps) * wq      over ALL H*D elements of a token's q at once (not per head);
+    k <- likewise with wk over all G*D       float32, plain weights
+    v <- (1 - lam) v + lam v_first           in layers that blend: v_first is what the first blending layer of
+                                             the model projected for the same token; lam a learned scalar
+    s_ij = scale * q_i . k_j                 no position enters the scores
+    j visible to i:  j <= i and (i - j < window or j < keep_first)
+    p_ij = exp(s_ij) / (1 + sum_j' exp(s_ij'))        a sink: one more key of score 0 that has no value
+    o_i  = (sum_j p_ij v_j) * sigmoid(g_i)   gate on the concatenated heads, from the same input h
+    y    = o Wo^T                            float32, to the norm that follows the branch
+
+Keys are cached normalised and values blended, so a later step reads them as they are. Every constant is a
+parameter; each option has an "off" value, so the part also serves designs that use only some of them.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..cache.cache import KVRequest
+from ..kernels import ops, trace
+from .base import AttentionOptions, Mixer, ParamSpec, register_mixer
+from .linear import Linear
+
+_DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm",
+                  "blend": "vmix"}
+
+
+class GatedAttention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, head_dim, v_head_dim, scale (None = 1/sqrt(head_dim)), window (0 = every
+    earlier key), keep_first, sink (bool), qk_norm_eps (None = no query/key norm), gate (bool), value_blend
+    (None, "first": leaves its projected values for later layers, or "blend": mixes them into its own),
+    blend_key (name under which the first layer's values travel through the step), names (overrides of the
+    tensors' checkpoint sub-names)."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        p = params
+        self.hidden, self.n_heads, self.n_kv_heads = int(p["hidden"]), int(p["n_heads"]), int(p["n_kv_heads"])
+        self.head_dim, self.v_head_dim = int(p["head_dim"]), int(p.get("v_head_dim") or p["head_dim"])
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"n_heads ({self.n_heads}) must be a multiple of n_kv_heads ({self.n_kv_heads})")
+        if max(self.head_dim, self.v_head_dim) > 256:
+            raise ValueError(f"head sizes {self.head_dim} / {self.v_head_dim} exceed what the attention kernels take (256)")
+        scale = p.get("scale")
+        self.window, self.keep_first = int(p.get("window") or 0), int(p.get("keep_first") or 0)
+        if not self.window:
+            self.keep_first = 0
+        self.options = AttentionOptions(scale=float(scale) if scale is not None else self.head_dim ** -0.5,
+                                        window=self.window, keep_first=self.keep_first, sink=bool(p.get("sink", False)))
+        self.qk_norm_eps = p.get("qk_norm_eps")
+        self.gate = bool(p.get("gate", False))
+        self.value_blend = p.get("value_blend")
+        if self.value_blend not in (None, "first", "blend"):
+            raise ValueError(f"value_blend must be None, 'first' or 'blend', got {self.value_blend!r}")
+        self.blend_key = str(p.get("blend_key", "first_values"))
+        self.names = dict(_DEFAULT_NAMES, **(p.get("names") or {}))
+        self.nq, self.nk = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        self.nv, self.no = self.n_kv_heads * self.v_head_dim, self.n_heads * self.v_head_dim
+        self.proj: Linear = None
+        self.o: Linear = None
+        self.q_w = self.k_w = self.lam = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d = self.names, self.hidden
+        specs = {n["q"]: ParamSpec((self.nq, d)), n["k"]: ParamSpec((self.nk, d)), n["v"]: ParamSpec((self.nv, d)),
+                 n["o"]: ParamSpec((d, self.no))}
+        if self.gate:
+            specs[n["gate"]] = ParamSpec((self.no, d))
+        if self.qk_norm_eps is not None:
+            specs[n["q_norm"]] = ParamSpec((self.nq,), role="vector", init=("ones",))
+            specs[n["k_norm"]] = ParamSpec((self.nk,), role="vector", init=("ones",))
+        if self.value_blend is not None:
+            # only a blending layer reads the scalar; a checkpoint may hold one for the first layer as well
+            specs[n["blend"]] = ParamSpec((), role="vector", init=("uniform", 0.2, 0.8),
+                                          optional=self.value_blend != "blend")
+        return specs
+
+    def load(self, tensors):
+        n = self.names
+        ws = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]] + ([tensors[n["gate"]]] if self.gate else [])
+        dtype = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0))
+        self.o = Linear(tensors[n["o"]])
+        if self.qk_norm_eps is not None:
+            self.q_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
+        if self.value_blend == "blend":
+            self.lam = tensors[n["blend"]].to(torch.float32).reshape(1).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.proj.nbytes() + self.o.nbytes() + (4 * (self.nq + self.nk) if self.q_w is not None else 0)
+
+    def cache_requests(self):
+        return [KVRequest(self.n_kv_heads, self.head_dim, self.window, v_head_dim=self.v_head_dim,
+                          keep_first=self.keep_first)]
+
+    def forward(self, x, ctx, unit, owns_cache, residual=None):
+        kv = unit.kv
+        T = x.shape[0]
+        trace.push("QKV_proj")
+        proj = self.proj(x)                                   # [T, q | k | v | gate]
+        trace.pop()
+        v_first = None
+        if self.value_blend == "first":
+            ctx.carry[self.blend_key] = proj[:, self.nq + self.nk:self.nq + self.nk + self.nv]
+        elif self.value_blend == "blend":
+            v_first = ctx.carry.get(self.blend_key)
+            if v_first is None:
+                raise RuntimeError(f"a layer blends its values with {self.blend_key!r}, but no earlier layer of this "
+                                   "step has left any")
+        trace.push("QKnorm+KV_cache")
+        q = torch.empty((T, self.nq), dtype=proj.dtype, device=proj.device)
+        ops.qk_norm_store(proj, q, kv.k, kv.v, self.q_w, self.k_w, float(self.qk_norm_eps or 0.0), ctx.tok_pos,
+                          ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, self.n_heads, self.n_kv_heads,
+                          self.head_dim, self.v_head_dim, owns_cache, lam=self.lam, v_first=v_first)
+        trace.pop()
+        out = torch.empty((T, self.no), dtype=proj.dtype, device=proj.device)
+        gate = proj[:, self.nq + self.nk + self.nv:] if self.gate else None
+        trace.push("FlashDecode" if ctx.decode else "FlashAttn")
+        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options, gate=gate)
+        trace.pop()
+        trace.push("Output_proj")
+        y = self.o(out, out_dtype=torch.float32)
+        trace.pop()
+        return y
+
+
+register_mixer("gated_attention", GatedAttention)

@@ -69,3 +69,7 @@ class Linear:
             return None
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
         return ops.gemm_skinny(x, self.weight, out, ops.SKINNY_SWIGLU)
+
+    def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int) -> Optional[torch.Tensor]:
+        """act(x W^T + bias) in one kernel, or None when no kernel for this shape exists."""
+        return None

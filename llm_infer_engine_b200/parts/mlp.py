@@ -68,3 +68,63 @@ class SwiGLU(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLU)
+
+
+class DenseMLP(FeedForward):
+    """down(act(up x + b_up)) + b_down: one up projection, a pointwise activation, one down projection.
+
+    params: hidden, intermediate, activation ("relu2" = the square of relu, "relu", "gelu_tanh", "silu"), bias (bool),
+    names (overrides of the checkpoint sub-names: up, up_bias, down, down_bias). The result is float32. A block
+    that adds the output bias inside its own next kernel calls `forward(..., defer_bias=True)` and reads
+    `down_bias` itself."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        name = str(params.get("activation", "relu2"))
+        if name not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {name!r} is not known ({sorted(ops.ACTIVATIONS)})")
+        self.activation = ops.ACTIVATIONS[name]
+        self.bias = bool(params.get("bias", True))
+        self.names = dict({"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b"},
+                          **(params.get("names") or {}))
+        self.up: Linear = None
+        self.down: Linear = None
+        self.up_bias = self.down_bias = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n = self.names
+        specs = {n["up"]: ParamSpec((self.intermediate, self.hidden)),
+                 n["down"]: ParamSpec((self.hidden, self.intermediate))}
+        if self.bias:
+            specs[n["up_bias"]] = ParamSpec((self.intermediate,), role="vector", init=("normal",))
+            specs[n["down_bias"]] = ParamSpec((self.hidden,), role="vector", init=("normal",))
+        return specs
+
+    def load(self, tensors):
+        n = self.names
+        self.up, self.down = Linear(tensors[n["up"]]), Linear(tensors[n["down"]])
+        if self.bias:
+            self.up_bias = tensors[n["up_bias"]].to(torch.float32).contiguous()
+            self.down_bias = tensors[n["down_bias"]].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.up.nbytes() + self.down.nbytes() + (4 * (self.intermediate + self.hidden) if self.bias else 0)
+
+    def forward(self, x, ctx, residual=None, defer_bias: bool = False):
+        trace.push("FFN")
+        try:
+            a = self.up.bias_act(x, self.up_bias, self.activation)      # product, bias and activation in one kernel
+            if a is None:
+                u = self.up(x)
+                a = torch.empty_like(u)
+                ops.bias_act(u, self.up_bias, a, self.activation)
+            y = self.down(a, out_dtype=torch.float32)
+            if self.down_bias is not None and not defer_bias:
+                ops.bias_act(y, self.down_bias, y, ops.ACT_NONE)
+            return y
+        finally:
+            trace.pop()
+
+
+register_feed_forward("dense_mlp", DenseMLP)

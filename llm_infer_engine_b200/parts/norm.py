@@ -14,19 +14,21 @@ from .base import DeferredNorm, Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
-    """params: size (width of a row), eps."""
+    """params: size (width of a row), eps; weight_name (the tensor's name under the part's checkpoint name,
+    default "weight"; "" = the part's name itself)."""
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), role="vector", init=tuple(self.params.get("init", ("ones",))))}
+        return {self.weight_name: ParamSpec((self.size,), role="vector", init=tuple(self.params.get("init", ("ones",))))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].to(torch.float32).contiguous()   # bf16 -> f32 is exact
+        self.weight = tensors[self.weight_name].to(torch.float32).contiguous()   # bf16 -> f32 is exact
 
     def weight_bytes(self) -> int:
         return self.size * 4
@@ -45,6 +47,13 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         trace.pop()
         return out
+
+
+    def add_normed(self, h, y, bias=None, act=None):
+        trace.push("RMSNorm")
+        ops.branch_norm_add(h, y, bias, self.weight, self.eps, act)
+        trace.pop()
+        return h
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -69,8 +69,9 @@ def compare(expected: Dict[str, tuple], found: Dict[str, tuple], ignore: List[st
 def load_weights(model: DecoderModel, model_dir: str) -> Dict[str, int]:
     files = open_model_files(model_dir)
     specs = model.param_specs()
-    expected = {n: ps.shape for n, ps in specs.items()}
     found = {n: f.entries[n][1] for n, f in files.items()}
+    specs = {n: ps for n, ps in specs.items() if n in found or not ps.optional}
+    expected = {n: ps.shape for n, ps in specs.items()}
     ignore = list(model.spec.ignore_unexpected)
     skipped = []
     head, emb = model.spec.head_name, model.spec.embedding_name
