@@ -57,37 +57,68 @@ __device__ __forceinline__ unsigned md_pack(float a, float b) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Merge of the runs of one (sequence, query head) by one warp.
+// Options beyond (scale, window), each off at 0 / null: the first keep_first keys of a sequence stay visible behind
+// the window; sink: one more softmax term of score 0 that has no value; gate: bfloat16 rows of n_q * HD elements,
+// gate_ld apart, whose sigmoid multiplies the output.
+struct MdOptions {
+  int keep_first;
+  int sink;
+  const __nv_bfloat16* gate;
+  int gate_ld;
+};
+
+// The last step of a (sequence, head)'s softmax: numerator and denominator relative to the maximum M (log2 units).
+// With a sink the denominator gains 2^(0 - M'), M' = max(M, 0).
+__device__ __forceinline__ float md_finish(float num, float den, float M, int sink) {
+  if (sink) {
+    const float Mx = fmaxf(M, 0.f);
+    const float f = md_exp2(M - Mx);
+    return num * f / (den * f + md_exp2(-Mx));
+  }
+  return num / den;
+}
+
+__device__ __forceinline__ float md_gated(float v, const __nv_bfloat16* gate_row, int d) {
+  return gate_row ? v / (1.f + __expf(-__bfloat162float(gate_row[d]))) : v;
+}
+
+// Merge of the runs of one (sequence, query head) by one warp. The runs that hold a visible key are 0..extra-1
+// (the kept first keys, where those lie in runs below the window's) and r0..r1.
 template <int HD>
 __device__ __forceinline__ void md_merge_head(const float* part_m, const float* part_l, const float* part_acc,
-                                              __nv_bfloat16* out_row, size_t base, int r0, int r1) {
+                                              __nv_bfloat16* out_row, size_t base, int r0, int r1, int extra, int sink,
+                                              const __nv_bfloat16* gate_row) {
   const int lane = threadIdx.x & 31;
+  const int n = extra + r1 - r0 + 1;
+  auto run_of = [&](int i) { return i < extra ? i : r0 + i - extra; };
   float M = -INFINITY;
-  for (int r = r0 + lane; r <= r1; r += 32) M = fmaxf(M, __ldcg(part_m + base + r));
+  for (int i = lane; i < n; i += 32) M = fmaxf(M, __ldcg(part_m + base + run_of(i)));
   M = warp_max(M);
   float denom = 0.f;
   float num[HD / 32];
 #pragma unroll
   for (int i = 0; i < HD / 32; ++i) num[i] = 0.f;
-  for (int c0 = r0; c0 <= r1; c0 += 32) {
-    const int r = c0 + lane;
+  for (int c0 = 0; c0 < n; c0 += 32) {
+    const int i_mine = c0 + lane;
     float w = 0.f;
-    if (r <= r1) {
+    if (i_mine < n) {
+      const int r = run_of(i_mine);
       w = md_exp2(__ldcg(part_m + base + r) - M);
       denom = fmaf(w, __ldcg(part_l + base + r), denom);
     }
-    const int n_here = min(32, r1 - c0 + 1);
+    const int n_here = min(32, n - c0);
 #pragma unroll 4
     for (int i = 0; i < n_here; ++i) {
       const float wi = __shfl_sync(0xffffffffu, w, i);
+      const size_t r = (size_t)run_of(c0 + i);
 #pragma unroll
-      for (int k = 0; k < HD / 32; ++k) num[k] = fmaf(wi, __ldcg(part_acc + (base + c0 + i) * HD + lane + 32 * k), num[k]);
+      for (int k = 0; k < HD / 32; ++k) num[k] = fmaf(wi, __ldcg(part_acc + (base + r) * HD + lane + 32 * k), num[k]);
     }
   }
   denom = warp_sum(denom);
-  const float inv = 1.f / denom;
 #pragma unroll
-  for (int k = 0; k < HD / 32; ++k) out_row[lane + 32 * k] = __float2bfloat16_rn(num[k] * inv);
+  for (int k = 0; k < HD / 32; ++k)
+    out_row[lane + 32 * k] = __float2bfloat16_rn(md_gated(md_finish(num[k], denom, M, sink), gate_row, lane + 32 * k));
 }
 
 // grid (n_runs, n_kv * chunks, n_seqs), chunks = ceil(G / 16); WARPS warps per block.
@@ -104,7 +135,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
                   float* __restrict__ part_acc, const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
                   const int* __restrict__ block_table, int max_pages, int n_q, int n_kv, float scale, int window,
                   int pages_per_run, int n_runs, int* __restrict__ counters, __nv_bfloat16* __restrict__ out,
-                  const float2* __restrict__ rope, int table_len, int q_ld, int write_kv) {
+                  const float2* __restrict__ rope, int table_len, int q_ld, int write_kv, MdOptions opt) {
   pdl_launch_dependents();
   constexpr int PITCH = HD + 8;                         // elements; rows 16 bytes apart in the banks
   constexpr int KS = HD / 16;                           // k-steps of Q K^T
@@ -124,7 +155,10 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
 
   const int len = seq_kvlen[seq];
   const int lo = md_first_visible(len, window);
-  const int p_first = max(run * pages_per_run, lo / kMdPage);
+  // keys [0, kept) are visible besides [lo, len): the kept first keys as far as the window has moved past them
+  const int kept = window > 0 ? min(opt.keep_first, lo) : 0;
+  const int kept_pages = (kept + kMdPage - 1) / kMdPage;
+  const int p_first = run * pages_per_run < kept_pages ? run * pages_per_run : max(run * pages_per_run, lo / kMdPage);
   const int p_last = min((run + 1) * pages_per_run - 1, (len - 1) / kMdPage);
   if (len <= 0 || p_first > p_last) return;
 
@@ -141,7 +175,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   // The warp's work is the sequence of half pages (p, h) of its pages that hold a visible key.
   auto visible = [&](int p, int h) {
     const int first = max(lo - p * kMdPage, 0), last = min(len - p * kMdPage, kMdPage);
-    return max(first, h * kHalf) < min(last, h * kHalf + kHalf);
+    return max(first, h * kHalf) < min(last, h * kHalf + kHalf) || p * kMdPage + h * kHalf < kept;
   };
   auto advance = [&](int& p, int& h) {
     do {
@@ -283,13 +317,14 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     // ---- scale, mask, running maximum and sum; probabilities relative to the new maximum
     const int first = max(lo - p * kMdPage, 0) - h * kHalf;
     const int last = min(len - p * kMdPage, kMdPage) - h * kHalf;       // visible keys of the half page: [first, last)
+    const int kept_here = kept - p * kMdPage - h * kHalf;               // and [0, kept_here): kept first keys
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int key = nt * 8 + 2 * t + c;
-        const bool vis = key >= first && key < last;
+        const bool vis = (key >= first && key < last) || key < kept_here;
         s[nt][c] = vis ? s[nt][c] * scale2 : -INFINITY;
         s[nt][2 + c] = vis ? s[nt][2 + c] * scale2 : -INFINITY;
         mx_lo = fmaxf(mx_lo, s[nt][c]);
@@ -386,7 +421,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     }
     const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
     if (n_runs == 1) {
-      out[head * HD + d] = __float2bfloat16_rn(num / den);
+      const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
+      out[head * HD + d] = __float2bfloat16_rn(md_gated(md_finish(num, den, M, opt.sink), gate_row, d));
     } else {
       part_acc[(head * n_runs + run) * HD + d] = num;
       if (d == 0) {
@@ -398,12 +434,13 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   if (n_runs == 1) return;
   // ---- the block that finishes last for this (sequence, head group) merges the runs
   const int r0 = (lo / kMdPage) / pages_per_run, r1 = ((len - 1) / kMdPage) / pages_per_run;
+  const int extra = min((kept_pages + pages_per_run - 1) / pages_per_run, r0);     // runs below r0 that hold kept keys
   __threadfence();                     // this block's partial results are visible before it is counted
   __syncthreads();
   if (threadIdx.x == 0) {
     int* c = counters + (size_t)seq * gridDim.y + blockIdx.y;
     const int done = atomicAdd(c, 1) + 1;
-    is_last = (done == r1 - r0 + 1);
+    is_last = (done == extra + r1 - r0 + 1);
     if (is_last) *c = 0;               // left clean for the next launch
   }
   __syncthreads();
@@ -411,7 +448,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   __threadfence();
   for (int row = warp; row < ng; row += WARPS) {
     const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
-    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1);
+    const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
+    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1, extra, opt.sink, gate_row);
   }
 }
 
@@ -420,7 +458,7 @@ static int launch_mma(const void* q, const void* k_cache, const void* v_cache, f
                       float* part_acc, const int* seq_slot, const int* seq_kvlen, const int* block_table, int max_pages,
                       int n_seqs, int n_q, int n_kv, float scale, int window, int pages_per_run, int n_runs,
                       int* counters, void* out, const float2* rope, int table_len, int q_ld, int write_kv,
-                      cudaStream_t stream) {
+                      MdOptions opt, cudaStream_t stream) {
   const int G = n_q / n_kv;
   const int chunks = (G + 15) / 16;
   const size_t smem = (size_t)WARPS * 2 * kMdPage * (HD + 8) * sizeof(__nv_bfloat16);
@@ -432,7 +470,7 @@ static int launch_mma(const void* q, const void* k_cache, const void* v_cache, f
   launch_k(decode_mma_kernel<HD, WARPS, ROPE>, dim3(n_runs, n_kv * chunks, n_seqs), dim3(WARPS * 32), smem, stream,
            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_m, part_l,
            part_acc, seq_slot, seq_kvlen, block_table, max_pages, n_q, n_kv, scale, window, pages_per_run, n_runs,
-           counters, (__nv_bfloat16*)out, rope, table_len, q_ld, write_kv);
+           counters, (__nv_bfloat16*)out, rope, table_len, q_ld, write_kv, opt);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -479,7 +517,8 @@ static int decode_mma_entry(const void* q, const void* k_cache, const void* v_ca
                             float* part_l, float* part_acc, int* counters, const int* seq_slot, const int* seq_kvlen,
                             const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
                             float scale, int window, int pages_per_run, int n_runs, const float2* rope, int table_len,
-                            int q_ld, int write_kv, cudaStream_t stream) {
+                            int q_ld, int write_kv, MdOptions opt, cudaStream_t stream) {
+  if (opt.keep_first < 0 || (opt.gate && opt.gate_ld < n_q * hd)) return LLMIE_ERR_BAD_ARG;
   if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || pages_per_run <= 0 || n_runs <= 0)
     return LLMIE_ERR_BAD_ARG;
   if (!llmie_attention_decode_mma_supported(hd, LLMIE_BF16, page_size)) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -512,10 +551,10 @@ static int decode_mma_entry(const void* q, const void* k_cache, const void* v_ca
 #define LLMIE_MMA(HD, W)                                                                                             \
   return rope ? launch_mma<HD, W, true>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,          \
                                         block_table, max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run,     \
-                                        n_runs, counters, out, rope, table_len, q_ld, write_kv, stream)              \
+                                        n_runs, counters, out, rope, table_len, q_ld, write_kv, opt, stream)         \
               : launch_mma<HD, W, false>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,         \
                                          block_table, max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run,    \
-                                         n_runs, counters, out, nullptr, 0, 0, 0, stream)
+                                         n_runs, counters, out, nullptr, 0, 0, 0, opt, stream)
   if (hd == 64) {
     if (best_w == 8) LLMIE_MMA(64, 8);
     if (best_w == 4) LLMIE_MMA(64, 4);
@@ -536,7 +575,19 @@ extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, co
                                           cudaStream_t stream) {
   return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
                           max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
-                          0, 0, stream);
+                          0, 0, MdOptions{0, 0, nullptr, 0}, stream);
+}
+
+// The same with the options of MdOptions: kept first keys, a sink, an output gate.
+extern "C" int llmie_attention_decode_mma_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             float* part_m, float* part_l, float* part_acc, int* counters,
+                                             const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                                             int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                                             float scale, int window, int pages_per_run, int n_runs, int keep_first,
+                                             int sink, const void* gate, int gate_ld, cudaStream_t stream) {
+  return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
+                          max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
+                          0, 0, MdOptions{keep_first, sink ? 1 : 0, (const __nv_bfloat16*)gate, gate_ld}, stream);
 }
 
 // The same with position encoding and the cache write inside: qkv bfloat16 [n_seqs, (n_q + 2 n_kv) hd] holds the
@@ -555,5 +606,5 @@ extern "C" int llmie_attention_decode_mma_rope(const void* qkv, void* k_cache, v
   return decode_mma_entry(qkv, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen,
                           block_table, max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs,
                           reinterpret_cast<const float2*>(rope), table_len, (n_q + 2 * n_kv) * hd, write_kv ? 1 : 0,
-                          stream);
+                          MdOptions{0, 0, nullptr, 0}, stream);
 }

@@ -114,7 +114,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, const int* __restrict__ block_table, int max_pages,
-                            int scratch_page, int n_q, int n_kv, float scale, int window, int* __restrict__ status) {
+                            int scratch_page, int n_q, int n_kv, float scale, int window, int keep_first, int sink,
+                            const __nv_bfloat16* __restrict__ gate, int gate_ld, int* __restrict__ status) {
   using Cfg = AttnCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
@@ -139,13 +140,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int last_key = start + t0 + rows_here - 1;
   const int first_key = (window > 0 && start + t0 - window + 1 > 0) ? start + t0 - window + 1 : 0;
   const int tile_lo = first_key / kKTile, tile_hi = last_key / kKTile;
-  const int n_tiles = tile_hi - tile_lo + 1;
+  // With kept first keys (keys below keep_first stay visible behind the window) the key tiles that hold them come
+  // first, as far as they lie below the window's tiles; then the window's tiles. tile_of(jt) is the key tile of step jt.
+  const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + kKTile - 1) / kKTile, tile_lo) : 0;
+  const int n_tiles = n_kept + tile_hi - tile_lo + 1;
+  auto tile_of = [&](int jt) { return jt < n_kept ? jt : tile_lo + jt - n_kept; };
 
   // One thread is the TMA producer. K and V of a key tile are the two cache pages that hold its 128 keys.
   const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
   auto load_k = [&](int jt) {
     const int ks = jt % Cfg::kKStages;
-    const int lp = (tile_lo + jt) * 2;           // logical pages of this key tile
+    const int lp = tile_of(jt) * 2;              // logical pages of this key tile
     const int last_page = last_key / 64;         // pages beyond the sequence's last key are not mapped
     const int pg0 = pages[lp];
     const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
@@ -158,7 +163,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   };
   auto load_v = [&](int jt) {
     const int vs = jt % Cfg::kVStages;
-    const int lp = (tile_lo + jt) * 2;
+    const int lp = tile_of(jt) * 2;
     const int last_page = last_key / 64;
     const int pg0 = pages[lp];
     const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
@@ -339,9 +344,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // instructions, a warp must never reach them with some of its lanes gone
       if (!__all_sync(0xffffffffu, mbar_wait(&sh.s_full[b], (jt / Cfg::kSBufs) & 1, abort))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
-      const int kbase = (tile_lo + jt) * kKTile + half * kCols;
-      const bool edge = ((tile_lo + jt) * kKTile + kKTile - 1 > start + t0) ||
-                        (window > 0 && (tile_lo + jt) * kKTile < start + t0 + kQTile - window);
+      const int tile = tile_of(jt);
+      const int kbase = tile * kKTile + half * kCols;
+      const bool edge = (tile * kKTile + kKTile - 1 > start + t0) ||
+                        (window > 0 && tile * kKTile < start + t0 + kQTile - window);
       // pass 1: the row's maximum over the keys it may see
       // (four running maxima and, below, four running sums: one chain of 64 dependent operations would be
       // what a row's time consists of)
@@ -355,11 +361,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (edge) {
           // A tile that the causal line or the window's far end crosses: the scores this row may not see become
           // -inf here, in tensor memory too, so that the second pass is the same for every tile (2^-inf = 0).
-          // Column c of this thread's half is seen if lo <= kbase + c <= qpos: one unsigned comparison.
+          // Column c of this thread's half is seen if lo <= kbase + c <= qpos (one unsigned comparison), or if
+          // it is one of the kept first keys: kbase + c < min(keep_first, qpos + 1).
           const unsigned span = (unsigned)(qpos - lo);
+          const int kept_rel = min(keep_first, qpos + 1) - kbase;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if ((unsigned)(c0 + i - lo_rel) > span) v[i] = 0xff800000u;
+            if ((unsigned)(c0 + i - lo_rel) > span && c0 + i >= kept_rel) v[i] = 0xff800000u;
             mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
           }
           tmem_st_32x32(lane_addr + b * 128 + half * kCols + c0, v);
@@ -441,13 +449,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
     }
     if (ok && r < rows_here) {
+      // the sink: one more term exp(0 - max) in the denominator (it has no value, the numerator stays);
+      // a maximum far below zero makes the term infinite and the output zero, which is the limit
+      if (sink) l_run += exp2_approx(-m_run * sl2);
       const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = out + ((size_t)(q_begin + t0 + r) * n_q + head) * HD + half * kOut;
+      const size_t row_off = ((size_t)(q_begin + t0 + r) * n_q + head) * HD + half * kOut;
+      __nv_bfloat16* dst = out + row_off;
+      const __nv_bfloat16* gr = gate ? gate + (size_t)(q_begin + t0 + r) * gate_ld + head * HD + half * kOut : nullptr;
 #pragma unroll
       for (int d = 0; d < kOut; d += 8) {
         float v8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
+        if (gr) {
+          float g8[8];
+          load8(gr + d, g8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v8[e] = __fdividef(v8[e], 1.f + __expf(-g8[e]));
+        }
         store8(dst + d, v8);
       }
     }
@@ -465,7 +484,8 @@ template <int HD>
 static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q,
                           const int* seq_slot, const int* seq_start, const int* block_table, int max_pages,
                           int n_pages_total, int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, float scale,
-                          int window, int* status, cudaStream_t stream) {
+                          int window, int keep_first, int sink, const void* gate, int gate_ld, int* status,
+                          cudaStream_t stream) {
   using Cfg = AttnCfg<HD>;
   CUtensorMap map_q, map_k, map_v;
   int rc = tc::make_tmap_bf16_2d(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_q * HD, (uint64_t)n_q * HD, kQTile);
@@ -481,7 +501,7 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
   dim3 grid(n_q, (max_q_len + kQTile - 1) / kQTile, n_seqs);
   attention_prefill_tc_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
       map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total - 1,
-      n_q, n_kv, scale, window, status);
+      n_q, n_kv, scale, window, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, status);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -498,23 +518,29 @@ extern "C" int llmie_attention_prefill_tc_supported(int hd, int page_size) {
 // caches: bfloat16 [n_pages_total, n_kv, 64, hd]; the LAST page (n_pages_total - 1) is a scratch
 // page that may be read for key positions nobody holds. seq_start[i]: tokens sequence i held
 // before this step (its new keys are already in the cache). max_q_len: longest new run, for the grid.
-// scale must be positive.
+// scale must be positive. Options, each off at 0 / null: keep_first (with a window: the first keys of a sequence stay
+// visible behind it), sink (one more softmax term of score 0 without a value), gate (bfloat16 rows of n_q * hd
+// elements, gate_ld apart, 16-byte aligned: the output is multiplied by sigmoid(gate)).
 extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* cu_q, const int* seq_slot, const int* seq_start,
                                           const int* block_table, int max_pages, int n_pages_total, int n_tokens,
                                           int n_seqs, int max_q_len, int n_q, int n_kv, int hd, float scale, int window,
-                                          int* status, cudaStream_t stream) {
+                                          int keep_first, int sink, const void* gate, int gate_ld, int* status,
+                                          cudaStream_t stream) {
   if (n_tokens < 0 || n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || n_pages_total <= 0)
     return LLMIE_ERR_BAD_ARG;
+  if (keep_first < 0 || (gate && (gate_ld < n_q * hd || gate_ld % 8 || !aligned16(gate)))) return LLMIE_ERR_BAD_ARG;
   if (!(scale > 0.f)) return LLMIE_ERR_BAD_ARG;   // the running maximum is taken before the scores are scaled
   if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
   if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (hd == 64)
     return launch_prefill<64>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
-                              n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, status, stream);
+                              n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate,
+                              gate_ld, status, stream);
   if (hd == 128)
     return launch_prefill<128>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
-                               n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, status, stream);
+                               n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate,
+                              gate_ld, status, stream);
   return LLMIE_ERR_UNSUPPORTED_SIZE;
 }

@@ -85,16 +85,6 @@ __global__ void branch_norm_add_kernel(float* __restrict__ h, const Y* __restric
 // ------------------------------------------------------------------------------------------
 // out[t, j] = act(u[t, j] + bias[j]); bias optional. Activations: 0 none, 1 relu, 2 relu squared, 3 gelu (tanh
 // form), 4 silu.
-__device__ __forceinline__ float apply_act(float z, int act) {
-  switch (act) {
-    case 1: return fmaxf(z, 0.f);
-    case 2: { const float r = fmaxf(z, 0.f); return r * r; }
-    case 3: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    case 4: return z / (1.f + expf(-z));
-    default: return z;
-  }
-}
-
 template <typename T, typename O>
 __global__ void bias_act_kernel(const T* __restrict__ u, const float* __restrict__ bias, O* __restrict__ out, int n,
                                 size_t total, int act) {

@@ -89,6 +89,18 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// Pointwise activations by code (shared with the Python wrappers): 0 none, 1 relu, 2 relu squared,
+// 3 gelu (tanh form), 4 silu.
+__device__ __forceinline__ float apply_act(float z, int act) {
+  switch (act) {
+    case 1: return fmaxf(z, 0.f);
+    case 2: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 3: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 4: return z / (1.f + expf(-z));
+    default: return z;
+  }
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Programmatic dependent launch: a kernel launched through launch_k may begin while the kernel

@@ -23,7 +23,7 @@ namespace llmie {
 
 constexpr int kSkUnroll = 4;     // 32-wide chunks of K a warp has in flight per round
 
-enum SkinnyEpilogue { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwiGLU = 3 };
+enum SkinnyEpilogue { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwiGLU = 3, kBiasAct = 4 };
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                                  unsigned b0, unsigned b1) {
@@ -50,7 +50,7 @@ __device__ __forceinline__ uint4 ldg16_stream(const void* p) {
 template <int NB, int EPI, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-                   int batch, int K, int ldo, int tile_stride, int hi_delta) {
+                   int batch, int K, int ldo, int tile_stride, int hi_delta, const float* __restrict__ bias, int act) {
   pdl_launch_dependents();
   __shared__ float red[WARPS][NB][16][8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,27 +194,32 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (EPI == kStoreBf16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
       if (EPI == kStoreF32) reinterpret_cast<float*>(out)[o] = v;
       if (EPI == kAddF32) reinterpret_cast<float*>(out)[o] += v;
+      if (EPI == kBiasAct)
+        reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(apply_act(bias ? v + bias[n] : v, act));
     }
   }
 }
 
 template <int NB, int WARPS>
 static int launch_epi(int epi, const void* x, const void* W, void* out, int batch, int K, int ldo, int tiles,
-                      int tile_stride, int hi_delta, cudaStream_t stream) {
+                      int tile_stride, int hi_delta, const float* bias, int act, cudaStream_t stream) {
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
   switch (epi) {
     case kStoreBf16:
-      launch_k(skinny_gemm_kernel<NB, kStoreBf16, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kStoreBf16, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta, bias, act);
       break;
     case kStoreF32:
-      launch_k(skinny_gemm_kernel<NB, kStoreF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kStoreF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta, bias, act);
       break;
     case kAddF32:
-      launch_k(skinny_gemm_kernel<NB, kAddF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kAddF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta, bias, act);
+      break;
+    case kBiasAct:
+      launch_k(skinny_gemm_kernel<NB, kBiasAct, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta, bias, act);
       break;
     case kSwiGLU:
-      launch_k(skinny_gemm_kernel<NB, kSwiGLU, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kSwiGLU, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta, bias, act);
       break;
     default:
       return LLMIE_ERR_BAD_ARG;
@@ -228,15 +233,15 @@ static int launch_epi(int epi, const void* x, const void* W, void* out, int batc
 // overlap with their neighbours' loads.
 template <int NB>
 static int launch_nb(int epi, const void* x, const void* W, void* out, int batch, int K, int ldo, int tiles,
-                     int tile_stride, int hi_delta, cudaStream_t stream) {
+                     int tile_stride, int hi_delta, const float* bias, int act, cudaStream_t stream) {
   const int chunks = K / 32;
   // An SM holds about 16 of these warps (registers). Doubling the warps of a block must leave every block
   // resident at once: 192 tiles of 16 warps would run as 148 blocks and then 44.
   int warps = 4;
   while (warps < 16 && tiles * warps * 2 <= 148 * 16 && chunks >= warps * 2 * kSkUnroll) warps *= 2;
-  if (warps >= 16) return launch_epi<NB, 16>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
-  if (warps >= 8) return launch_epi<NB, 8>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
-  return launch_epi<NB, 4>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
+  if (warps >= 16) return launch_epi<NB, 16>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
+  if (warps >= 8) return launch_epi<NB, 8>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
+  return launch_epi<NB, 4>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
 }
 
 }  // namespace llmie
@@ -249,10 +254,11 @@ extern "C" int llmie_gemm_skinny_max_batch(void) { return 32; }
 // x [batch, K] bfloat16, W [N, K] bfloat16 (for epilogue 3: W = [gate rows; up rows], N = 2 * ff).
 // epilogue 0: out bfloat16 [batch, ldo] = y      1: out float32 [batch, ldo] = y
 //          2: out float32 [batch, ldo] += y      3: out bfloat16 [batch, ldo] = silu(gate) * up, ff columns
+//          4: out bfloat16 [batch, ldo] = act(y + bias), bias float32 [N] or null, act a code of apply_act
 // Needs K % 32 == 0, N % 16 == 0 (epilogue 3: ff % 8 == 0), 16-byte aligned x and W.
-extern "C" int llmie_gemm_skinny(const void* x, const void* W, void* out, int batch, int N, int K, int ldo,
-                                 int epilogue, cudaStream_t stream) {
-  if (batch < 0 || N <= 0 || K <= 0) return LLMIE_ERR_BAD_ARG;
+static int gemm_skinny_entry(const void* x, const void* W, void* out, int batch, int N, int K, int ldo, int epilogue,
+                             const float* bias, int act, cudaStream_t stream) {
+  if (batch < 0 || N <= 0 || K <= 0 || act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
   if (batch > 32) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (K % 32) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (!aligned16(x) || !aligned16(W)) return LLMIE_ERR_ALIGNMENT;
@@ -265,7 +271,19 @@ extern "C" int llmie_gemm_skinny(const void* x, const void* W, void* out, int ba
     tiles = N / 16; tile_stride = 16; hi_delta = 8;
   }
   if (batch == 0) return LLMIE_OK;
-  if (batch <= 8) return launch_nb<1>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
-  if (batch <= 16) return launch_nb<2>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
-  return launch_nb<4>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
+  if (batch <= 8) return launch_nb<1>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
+  if (batch <= 16) return launch_nb<2>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
+  return launch_nb<4>(epilogue, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, bias, act, stream);
+}
+
+extern "C" int llmie_gemm_skinny(const void* x, const void* W, void* out, int batch, int N, int K, int ldo,
+                                 int epilogue, cudaStream_t stream) {
+  if (epilogue == kBiasAct) return LLMIE_ERR_BAD_ARG;
+  return gemm_skinny_entry(x, W, out, batch, N, K, ldo, epilogue, nullptr, 0, stream);
+}
+
+// out bfloat16 [batch, ldo] = act(x W^T + bias) in one kernel.
+extern "C" int llmie_gemm_skinny_bias_act(const void* x, const void* W, void* out, int batch, int N, int K, int ldo,
+                                          const float* bias, int act, cudaStream_t stream) {
+  return gemm_skinny_entry(x, W, out, batch, N, K, ldo, kBiasAct, bias, act, stream);
 }

@@ -60,12 +60,9 @@ class StepContext:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own
         sequence up to its own position (and no further back than `options.window`, if set, except the first
         `options.keep_first` keys). The value head size is the cache's. With `gate` ([T, n_q * value head size],
-        possibly a column slice) the output is multiplied by sigmoid(gate), inside the attention kernel where it
-        can do that, else by a kernel of its own."""
+        possibly a column slice) the output is multiplied by sigmoid(gate) inside the attention kernel."""
         plan = self.kernels
-        if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, options):
-            if gate is not None:
-                ops.sigmoid_gate(out, gate)
+        if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, options, gate):
             return
         ops.attention_paged(q, kv.k, kv.v, out, self.tok_pos, self.tok_seq, self.seq_slot, kv.block_table,
                             kv.page_size, n_q, n_kv, head_dim, options.scale, options.window, options.keep_first,

@@ -52,12 +52,20 @@ class KernelPlan:
                                       write_kv, counters=counters)
         return True
 
-    def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options) -> bool:
-        """Returns True when a specialised kernel ran. Every kernel below takes the options there are
-        today (scale, window); a new option is checked here, kernel by kernel."""
+    def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate=None) -> bool:
+        """Returns True when a specialised kernel ran (the gate, if any, applied). The tensor-core kernels know
+        every option (scale, window, kept first keys, sink, gate); the CUDA-core split-KV kernel knows scale and
+        window. A value head size that differs from the key head size is the plain kernel's alone."""
         scale, window = options.scale, options.window
-        if not options.plain or kv.v.shape[-1] != head_dim:
-            return False       # kept first keys, a sink or a value head size of its own: the plain kernel knows them
+        if kv.v.shape[-1] != head_dim:
+            return False
+        if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16):
+            # the tensor-core kernels load the gate 16 bytes at a time: rows that do not start on 16 bytes are
+            # applied by a kernel of their own afterwards
+            if not self.attention(ctx, q, kv, out, n_q, n_kv, head_dim, options, None):
+                return False
+            ops.sigmoid_gate(out, gate)
+            return True
         if ctx.decode and self.decode_attention != "split" \
                 and ops.attention_decode_mma_supported(head_dim, q.dtype, kv.page_size):
             # bfloat16, head size 64 or 128: a warp per page on the tensor cores
@@ -65,17 +73,21 @@ class KernelPlan:
             n_runs = ((ctx.max_kv_len + 63) // 64 + pages - 1) // pages
             counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
             ops.attention_decode_mma(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
-                                     n_q, n_kv, head_dim, scale, window, pages, n_runs, counters=counters)
+                                     n_q, n_kv, head_dim, scale, window, pages, n_runs, counters=counters,
+                                     keep_first=options.keep_first, sink=options.sink, gate=gate)
             return True
-        if ctx.decode and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
+        if ctx.decode and options.plain and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
             n_runs = (ctx.max_kv_len + run - 1) // run
             counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
             ops.attention_decode(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
                                  n_q, n_kv, head_dim, scale, window, run, n_runs, counters=counters)
+            if gate is not None:
+                ops.sigmoid_gate(out, gate)
             return True
         if not ctx.decode and scale > 0 and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
             ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
-                                     kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, scale, window)
+                                     kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, scale, window,
+                                     options.keep_first, options.sink, gate)
             return True
         return False

@@ -528,11 +528,14 @@ def attention_decode_mma_pages(n_seqs: int, n_q: int, n_kv: int, max_kv_len: int
 
 def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table, page_size: int, n_q: int,
                          n_kv: int, head_dim: int, scale: float, window: int, pages_per_run: int, n_runs: int,
-                         counters: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None):
+                         counters: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None,
+                         keep_first: int = 0, sink: bool = False, gate: Optional[torch.Tensor] = None):
     """Attention for a one-token step on the tensor cores (bfloat16): a warp per cache page, the warps of a
     block merged in shared memory. Arguments as attention_decode; n_runs * pages_per_run pages must cover
-    the longest sequence. With n_runs == 1 neither scratch nor counters are touched."""
+    the longest sequence. With n_runs == 1 neither scratch nor counters are touched. keep_first, sink and gate
+    as in attention_paged."""
     n = q.shape[0]
+    gate_ld = _row_slice(gate, "gate", torch.bfloat16, n, n_q * head_dim) if gate is not None else 0
     _need(q, "q", torch.bfloat16, (n, n_q * head_dim))
     _need(out, "out", torch.bfloat16, (n, n_q * head_dim))
     _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
@@ -555,12 +558,13 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
         _need(counters, "counters", torch.int32)
         base, n_ml, cptr = scratch.data_ptr(), n * n_q * n_runs, counters.data_ptr()
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
-    f = _fn("attention_decode_mma", "llmie_attention_decode_mma",
-            [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 3 + [_c_void_p])
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_ex",
+            [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 5 + [_c_void_p, _c_int, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base or None,
              (base + 4 * n_ml) or None, (base + 8 * n_ml) or None, cptr, seq_slot.data_ptr(), seq_kvlen.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale),
-             int(window), int(pages_per_run), int(n_runs), _stream()), "attention_decode_mma")
+             int(window), int(pages_per_run), int(n_runs), int(keep_first), 1 if sink else 0, _ptr(gate), gate_ld,
+             _stream()), "attention_decode_mma")
     return out
 
 
@@ -664,6 +668,25 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     _work(_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1])
     f = _fn("gemm_skinny", "llmie_gemm_skinny", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), batch, N, K, cols, epilogue, _stream()), "gemm_skinny")
+    return out
+
+
+def gemm_skinny_bias_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                         act: int) -> torch.Tensor:
+    """out (bfloat16 [batch, N]) = act(x w^T + bias) in one kernel, for a few rows of x; bias float32 [N] or None."""
+    batch, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (N, K))
+    _need(out, "out", torch.bfloat16, (batch, N))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (N,))
+    if not gemm_skinny_ok(batch, N, K):
+        raise KernelError(f"gemm_skinny_bias_act: shape batch={batch}, N={N}, K={K} is not supported")
+    _work(_nbytes(x, w, out), 2.0 * batch * N * K)
+    f = _fn("gemm_skinny", "llmie_gemm_skinny_bias_act", [_c_void_p] * 3 + [_c_int] * 4 + [_c_void_p, _c_int, _c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), batch, N, K, N, _ptr(bias), int(act), _stream()),
+           "gemm_skinny_bias_act")
     return out
 
 
@@ -778,12 +801,17 @@ def attention_prefill_tc_supported(head_dim: int, page_size: int, dtype: torch.d
 
 def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, page_size: int,
                          n_seqs: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
-                         window: int = 0):
+                         window: int = 0, keep_first: int = 0, sink: bool = False,
+                         gate: Optional[torch.Tensor] = None):
     """Causal attention for runs of new tokens on the tcgen05 tensor cores, K and V read from the
     paged cache by TMA. q, out bfloat16 [T, n_q hd] with sequences packed (cu_q int32 [n + 1]);
     seq_start int32 [n]: tokens each sequence held before this step. The caches' last page must be
-    a scratch page. head_dim 64 or 128, pages of 64."""
+    a scratch page. head_dim 64 or 128, pages of 64. keep_first, sink and gate as in attention_paged (the gate's
+    rows must start on 16 bytes)."""
     T = q.shape[0]
+    gate_ld = _row_slice(gate, "gate", torch.bfloat16, T, n_q * head_dim) if gate is not None else 0
+    if gate is not None and (gate_ld % 8 or gate.data_ptr() % 16):
+        raise KernelError("attention_prefill_tc: the gate's rows must start on 16-byte boundaries")
     _need(q, "q", torch.bfloat16, (T, n_q * head_dim))
     _need(out, "out", torch.bfloat16, (T, n_q * head_dim))
     _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
@@ -798,11 +826,12 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
         raise KernelError(f"attention_prefill_tc: the scale must be positive, got {scale}")
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc",
-            [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p, _c_void_p])
+            [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),
              seq_slot.data_ptr(), seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1],
-             k_cache.shape[0], T, n_seqs, max_q_len, n_q, n_kv, head_dim, float(scale), int(window),
-             tc_status_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+             k_cache.shape[0], T, n_seqs, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), int(keep_first),
+             1 if sink else 0, _ptr(gate), gate_ld, tc_status_word(q.device).data_ptr(), _stream()),
+           "attention_prefill_tc")
     return out
 
 

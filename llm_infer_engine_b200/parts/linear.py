@@ -71,5 +71,11 @@ class Linear:
         return ops.gemm_skinny(x, self.weight, out, ops.SKINNY_SWIGLU)
 
     def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int) -> Optional[torch.Tensor]:
-        """act(x W^T + bias) in one kernel, or None when no kernel for this shape exists."""
-        return None
+        """act(x W^T + bias) in one kernel (bfloat16, up to SKINNY_BEST_BATCH rows), or None when no kernel for
+        this shape exists."""
+        if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+            return None
+        if x.shape[0] > ops.SKINNY_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features, self.in_features):
+            return None
+        out = torch.empty((x.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        return ops.gemm_skinny_bias_act(x, self.weight, bias, out, act)

@@ -39,8 +39,9 @@ def engine_for(tag, dtype, **kw):
 
 def bound(dtype, want):
     """float32 agrees to rounding. bfloat16 rounds every activation between kernels; its bound is a share of the
-    request's largest logit, several times below what a lost or added key changes on these sharpened models."""
-    return (3e-5 if dtype == "float32" else 0.06) * max(1.0, float(want.abs().max()))
+    request's largest logit (scores this sharp carry the rounding of q and k into the weights), several times below
+    what a lost or added key changes on these models."""
+    return (3e-5 if dtype == "float32" else 0.1) * max(1.0, float(want.abs().max()))
 
 
 def oracle(tag, requests):
@@ -274,6 +275,42 @@ def test_sink_takes_its_share_and_gate_scales_the_output(dtype):
     assert float((out.float() - want).abs().max()) <= (1e-5 if dtype == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_decode_attention_in_runs_with_kept_keys_sink_and_gate(hd):
+    """The tensor-core decode kernel cut into runs of 1, 2, 3 and 5 pages (runs below the window hold only the
+    kept first keys, runs in between hold nothing and are skipped) against the plain kernel, for sequences of
+    unequal lengths, some shorter than the window or than the kept prefix."""
+    from llm_infer_engine_b200.cache import Cache, KVRequest
+    from llm_infer_engine_b200.kernels import ops
+    n_q, n_kv = 8, 2
+    lens = [700, 64, 65, 130, 3, 391]
+    cache = Cache([[KVRequest(n_kv, hd, 150, keep_first=70)]], len(lens), 64 * 40, 1024, torch.bfloat16, DEV)
+    slots = [cache.take_slot() for _ in lens]
+    for s_, l in zip(slots, lens):
+        cache.reserve(s_, l)
+    kv = cache.unit(0).kv
+    g = torch.Generator().manual_seed(21)
+    kv.k.copy_((torch.randn(kv.k.shape, generator=g) * 0.5).to(DEV, torch.bfloat16))
+    kv.v.copy_(torch.randn(kv.v.shape, generator=g).to(DEV, torch.bfloat16))
+    q = torch.randn(len(lens), n_q * hd, generator=g).to(DEV, torch.bfloat16)
+    gate = torch.randn(len(lens), n_q * hd + 16, generator=g).to(DEV, torch.bfloat16)
+    ctx = make_ctx([1] * len(lens), [l - 1 for l in lens], slots, "bfloat16")
+    for window, keep, sink, gated in [(150, 70, True, True), (150, 70, False, False), (64, 130, True, False),
+                                      (0, 0, True, True), (300, 1, False, True)]:
+        gt = gate[:, 8:8 + n_q * hd] if gated else None
+        want = torch.empty_like(q)
+        ops.attention_paged(q, kv.k, kv.v, want, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.block_table, 64, n_q, n_kv,
+                            hd, 0.2, window, keep, sink, gt)
+        for pages in (1, 2, 3, 5, 16):
+            n_runs = (max(lens) + 64 * pages - 1) // (64 * pages)
+            out = torch.empty_like(q)
+            counters = torch.zeros(ops.decode_counter_ints(len(lens), n_q, n_kv), dtype=torch.int32, device=DEV)
+            ops.attention_decode_mma(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, 64, n_q, n_kv, hd,
+                                     0.2, window, pages, n_runs, counters=counters, keep_first=keep, sink=sink, gate=gt)
+            assert float((out.float() - want.float()).abs().max()) < 2e-2, (window, keep, sink, gated, pages)
+            assert int(counters.abs().sum()) == 0
+
+
 # ------------------------------------------------------------------------------------------ the engine
 LENGTHS = {"a": [1, 2, 43, 44, 64, 65, 130, 300], "b": [3, 8, 33, 34, 100, 128, 129, 380], "c": [5, 71, 151, 215, 64, 700]}
 
@@ -307,7 +344,8 @@ def test_every_schedule_matches_plain(tag, dtype):
 
 def test_the_models_are_sharp_enough_to_show_a_mask_that_is_one_off():
     """The bounds above mean something only if a window or a kept prefix that is one token off moves the logits
-    by more than they allow: the plain implementation with such a mask must differ by several bounds."""
+    by more than they allow: the plain implementation with such a mask must differ by several bounds (here:
+    at least three of the bfloat16 bound, which is thousands of the float32 bound)."""
     for tag in ("a", "b", "c"):
         w, cfg = helpers.plain_weights(folder_for(tag)), CFGS[tag]
         toks = helpers.random_tokens(cfg["vocab"], max(LENGTHS[tag]), seed=47)
@@ -319,7 +357,7 @@ def test_the_models_are_sharp_enough_to_show_a_mask_that_is_one_off():
                     layer["mixer"]["mask"][change[0]] = max(0, layer["mixer"]["mask"][change[0]] + change[1])
             wrong = plain.logits(w, off, toks)
             gap = float((wrong - right).abs().max())
-            assert gap > 4 * bound("bfloat16", right), (tag, what, gap, bound("bfloat16", right))
+            assert gap > 3 * bound("bfloat16", right), (tag, what, gap, bound("bfloat16", right))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
