@@ -386,6 +386,104 @@ def run_per_kernel(args, engine, pk: dict) -> str:
     return "\n".join(parts)
 
 
+# ------------------------------------------------------------------------------------------ two designs side by side
+def zemivik_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int, n_layers: int,
+                   window: int, keep_first: int) -> dict:
+    """A Zemivik configuration with a Llama shape's layer sizes (window 0 = no mask: every earlier token)."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+             "v_mix": True, "mask": {"size": window, "keep_first": keep_first} if window else None}
+    return {"architecture": "Zemivik", "vocab": vocab, "width": width, "max_positions": CONTEXT,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": ff}}
+                       for _ in range(n_layers)]}
+
+
+def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
+    """Per-kernel tables (eager steps, CUDA events) of a decode step at `batch` sequences and of a 2,048-token
+    prompt."""
+    import torch
+    from llm_infer_engine_b200.kernels import ops, trace
+    n_steps = 8
+    prompts = random_prompts([PROMPT_LEN] * batch, engine.vocab_size, seed=10 + batch)
+    slots = [engine.open() for _ in range(batch)]
+    logits = engine.step(slots, prompts, "last")
+    tokens = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    ops.sample(logits, tokens)
+    for _ in range(3):
+        logits = engine.step(slots, [[t] for t in tokens.tolist()], "last")
+        ops.sample(logits, tokens)
+    with trace.timing() as timer:
+        for _ in range(n_steps):
+            logits = engine.step(slots, [[t] for t in tokens.tolist()], "last")
+            ops.sample(logits, tokens)
+        rows = timer.table()
+    for s_ in slots:
+        engine.close(s_)
+    parts = [kernel_table(rows, n_steps, pk, f"{title}: decode, batch {batch}, context about {PROMPT_LEN + 8}")]
+    prompt = random_prompts([PREFILL_TOKENS], engine.vocab_size, seed=99)[0]
+    for _ in range(3):
+        slot = engine.open()
+        engine.step([slot], [prompt], "last")
+        engine.close(slot)
+    with trace.timing() as timer:
+        for _ in range(3):
+            slot = engine.open()
+            engine.step([slot], [prompt], "last")
+            engine.close(slot)
+        rows = timer.table()
+    parts.append(kernel_table(rows, 3, pk, f"{title}: prefill, one prompt of {PREFILL_TOKENS} tokens"))
+    return "\n".join(parts)
+
+
+def run_designs(args, pk: dict) -> str:
+    """Zemivik beside Llama at equal layer sizes (random weights, bfloat16): decode throughput at batch 1, 8 and 64
+    after 512-token prompts (captured steps, device time), prefill throughput of one 2,048-token prompt, and the
+    per-kernel tables of both. Zemivik once without a mask (the attention work of Llama's) and once with a window
+    of 1,024 tokens that keeps the first four. The shared vocabulary is kept small so that the layers, not the
+    head, are what is compared."""
+    import torch
+    from llm_infer_engine_b200 import Engine, write_random_model
+    from llm_infer_engine_b200.weights import scratch_folder
+    n_layers = args.layers or 4
+    vocab = 32000
+    shapes = [("1B layer sizes", CONFIG_1B), ("8B layer sizes", CONFIG_8B)]
+    steps = min(args.steps, 64)
+    lines = [f"Zemivik beside Llama at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
+             f"(peaks: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s, {pk['source']}).", "",
+             "| layer sizes | design | decode b1 tok/s | ms/step | decode b8 tok/s | ms/step | decode b64 tok/s | ms/step | "
+             f"prefill {PREFILL_TOKENS} tok/s | ms |", "|---|---|---|---|---|---|---|---|---|---|"]
+    tables = []
+    for name, base in shapes:
+        d, hq, hkv, hd, ff = (base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"],
+                              base["head_dim"], base["intermediate_size"])
+        llama = dict(base, vocab_size=vocab, num_hidden_layers=n_layers, tie_word_embeddings=False, bos_token_id=1,
+                     eos_token_id=2)
+        designs = [("Llama", llama),
+                   ("Zemivik, no mask", zemivik_config(d, hq, hkv, hd, ff, vocab, n_layers, 0, 0)),
+                   ("Zemivik, window 1024 + 4", zemivik_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024, 4))]
+        for design, cfg in designs:
+            folder = scratch_folder("llmie_bench_design_")
+            write_random_model(cfg, folder, seed=3, std=0.02)
+            per_seq = PROMPT_LEN + steps + args.warmup + 64
+            engine = Engine(folder, dtype="bfloat16", device=0, max_batch=64, max_seq_len=CONTEXT,
+                            max_tokens=max(64 * ((per_seq + 63) // 64 * 64), PREFILL_TOKENS + 64), cuda_graph=True)
+            drop_folder(folder)
+            cells = []
+            for batch in (1, 8, 64):
+                sec, _, _ = time_decode(engine, batch, PROMPT_LEN, steps, max(args.warmup, 3), seed=batch)
+                cells += [f"{batch * steps / sec:,.0f}", f"{1e3 * sec / steps:.3f}"]
+            t = time_prefill(engine, PREFILL_TOKENS, warmup=3, reps=5, seed=7)
+            cells += [f"{PREFILL_TOKENS / t:,.0f}", f"{1e3 * t:.2f}"]
+            lines.append(f"| {name} | {design} | " + " | ".join(cells) + " |")
+            print(f"[bench] {name} / {design}: {cells}", file=sys.stderr)
+            if design != "Zemivik, no mask":
+                engine.use_cuda_graph = False
+                tables.append(step_tables(engine, pk, f"{name}, {design}"))
+            del engine
+            torch.cuda.empty_cache()
+    return "\n".join(lines) + "\n\n" + "\n".join(tables)
+
+
 # ------------------------------------------------------------------------------------------ attention kernels alone
 def attention_sweep(heads: int, kv_heads: int, head_dim: int, pk: dict) -> str:
     """The two attention kernels alone, at several batch sizes and context lengths, against the measured peaks:
@@ -479,6 +577,13 @@ def run_ours(args):
     pk = peaks()
     if args.attention_sweep:
         text = attention_sweep(args.heads, args.kv_heads, args.head_dim, pk)
+        print(text)
+        if args.per_kernel_out:
+            with open(args.per_kernel_out, "w", encoding="utf-8") as f:
+                f.write(text + "\n")
+        return 0
+    if args.designs:
+        text = run_designs(args, pk)
         print(text)
         if args.per_kernel_out:
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
@@ -647,6 +752,9 @@ def main():
     ap.add_argument("--per-kernel-out", default="", help="write the per-kernel tables to this file as well")
     ap.add_argument("--attention-sweep", action="store_true",
                     help="time the two attention kernels alone at several batch sizes and contexts; prints a table")
+    ap.add_argument("--designs", action="store_true",
+                    help="Zemivik beside Llama at equal layer sizes: decode and prefill throughput and per-kernel tables "
+                         "(prints markdown; --layers sets the depth, default 4)")
     ap.add_argument("--heads", type=int, default=32, help="query heads of --attention-sweep")
     ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of --attention-sweep")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="head size of --attention-sweep")

@@ -82,6 +82,47 @@ __global__ void branch_norm_add_kernel(float* __restrict__ h, const Y* __restric
   }
 }
 
+// The same for rows of at most 8 * 1024 elements with d % 8 == 0: a thread owns one run of 8 elements, kept in
+// registers between the two passes, with 16-byte loads and stores.
+template <typename Y, typename A>
+__global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const Y* __restrict__ y,
+                                           const float* __restrict__ bias, const float* __restrict__ w, float eps,
+                                           A* __restrict__ act, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int i = threadIdx.x * 8;
+  const bool active = i < d;
+  float x[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) x[e] = 0.f;
+  if (active) {
+    load8(y + (size_t)t * d + i, x);
+    if (bias) {
+      float b[8];
+      load8(bias + i, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] += b[e];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)d + eps);
+  if (active) {
+    float wv[8], hv[8];
+    load8(w + i, wv);
+    float* hr = h + (size_t)t * d + i;
+    load8(hr, hv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hv[e] += x[e] * rstd * wv[e];
+    store8(hr, hv);
+    if (act) store8(act + (size_t)t * d + i, hv);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // out[t, j] = act(u[t, j] + bias[j]); bias optional. Activations: 0 none, 1 relu, 2 relu squared, 3 gelu (tanh
 // form), 4 silu.
@@ -96,6 +137,27 @@ __global__ void bias_act_kernel(const T* __restrict__ u, const float* __restrict
     float z = to_f32(u[i]);
     if (bias) z += bias[i % n];
     out[i] = from_f32<O>(apply_act(z, act));
+  }
+}
+
+// The same, eight outputs a thread with 16-byte loads (n % 8 == 0): grid (column blocks, rows), no index division.
+template <typename T, typename O>
+__global__ void bias_act_vec_kernel(const T* __restrict__ u, const float* __restrict__ bias, O* __restrict__ out, int n8,
+                                    int n_tokens, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int j8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j8 >= n8) return;
+  float b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) b[e] = 0.f;
+  if (bias) load8(bias + (size_t)j8 * 8, b);
+  for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+    float z[8];
+    load8(u + ((size_t)t * n8 + j8) * 8, z);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) z[e] = apply_act(z[e] + b[e], act);
+    store8(out + ((size_t)t * n8 + j8) * 8, z);
   }
 }
 
@@ -184,6 +246,94 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ proj, int ld, T* __re
   }
 }
 
+// The same with 16-byte loads and stores, for head sizes and a row pitch that are multiples of 8 (and 16-byte
+// aligned tensors): a thread owns runs of 8 elements; a token's q, k and v are read once for the sums of squares
+// and once more (from L1) for the stores.
+template <typename T>
+__global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out,
+                                         T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                         const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                         const float* __restrict__ lam_ptr, const T* __restrict__ v_first,
+                                         int v_first_ld, const int* __restrict__ tok_pos,
+                                         const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                         const int* __restrict__ block_table, int max_pages, int page_size, int n_q,
+                                         int n_kv, int hd, int hdv, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int nq = n_q * hd, nk = n_kv * hd, nv = n_kv * hdv;
+  const T* qs = proj + (size_t)t * ld;
+  const T* ks = qs + nq;
+  const T* vs = ks + nk;
+  float rq = 1.f, rk = 1.f;
+  if (q_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < nq; i += blockDim.x * 8) {
+      float x[8];
+      load8(qs + i, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    }
+    ss = block_sum(ss, red);
+    rq = 1.f / sqrtf(ss / (float)nq + eps);
+  }
+  if (k_w && write_kv) {
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < nk; i += blockDim.x * 8) {
+      float x[8];
+      load8(ks + i, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    }
+    ss = block_sum(ss, red);
+    rk = 1.f / sqrtf(ss / (float)nk + eps);
+  }
+  T* qo = q_out + (size_t)t * nq;
+  for (int i = threadIdx.x * 8; i < nq; i += blockDim.x * 8) {
+    float x[8];
+    load8(qs + i, x);
+    if (q_w) {
+      float w8[8];
+      load8(q_w + i, w8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = x[e] * rq * w8[e];
+    }
+    store8(qo + i, x);
+  }
+  if (!write_kv) return;
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+  const int in_page = pos % page_size;
+  for (int i = threadIdx.x * 8; i < nk; i += blockDim.x * 8) {
+    const int hk = i / hd, e0 = i - hk * hd;
+    float x[8];
+    load8(ks + i, x);
+    if (k_w) {
+      float w8[8];
+      load8(k_w + i, w8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = x[e] * rk * w8[e];
+    }
+    store8(k_cache + (((size_t)page * n_kv + hk) * page_size + in_page) * hd + e0, x);
+  }
+  const float lam = v_first ? *lam_ptr : 0.f;
+  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
+  for (int i = threadIdx.x * 8; i < nv; i += blockDim.x * 8) {
+    const int hk = i / hdv, e0 = i - hk * hdv;
+    float x[8];
+    load8(vs + i, x);
+    if (vf) {
+      float f[8];
+      load8(vf + i, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = to_f32(from_f32<T>((1.f - lam) * x[e] + lam * f[e]));
+    }
+    store8(v_cache + (((size_t)page * n_kv + hk) * page_size + in_page) * hdv + e0, x);
+  }
+}
+
 template <typename A> struct DT { };
 template <> struct DT<float> { static constexpr int code = LLMIE_F32; };
 template <> struct DT<__nv_bfloat16> { static constexpr int code = LLMIE_BF16; };
@@ -232,14 +382,17 @@ extern "C" int llmie_branch_norm_add(float* h, const void* y, int y_dtype, const
   if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (y_dtype != LLMIE_BF16 && y_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
   if (act && act_dtype != LLMIE_BF16 && act_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
-  const dim3 grid(n_tokens), block(row_threads(d));
+  const bool vec = d % 8 == 0 && d <= 8 * 1024 && aligned16(h) && aligned16(y) && aligned16(w) &&
+                   (!bias || aligned16(bias)) && (!act || aligned16(act));
+  const dim3 grid(n_tokens), block(vec ? ((d / 8 + 31) / 32) * 32 : row_threads(d));
 #define LLMIE_BNA(Y, A)                                                                                          \
-  launch_k(branch_norm_add_kernel<Y, A>, grid, block, smem, stream, h, (const Y*)y, bias, w, eps, (A*)act, d)
+  if (vec) launch_k(branch_norm_add_vec_kernel<Y, A>, grid, block, 0, stream, h, (const Y*)y, bias, w, eps, (A*)act, d); \
+  else launch_k(branch_norm_add_kernel<Y, A>, grid, block, smem, stream, h, (const Y*)y, bias, w, eps, (A*)act, d)
   const bool y_bf16 = y_dtype == LLMIE_BF16, act_bf16 = act && act_dtype == LLMIE_BF16;
-  if (y_bf16 && act_bf16) LLMIE_BNA(__nv_bfloat16, __nv_bfloat16);
-  else if (y_bf16) LLMIE_BNA(__nv_bfloat16, float);
-  else if (act_bf16) LLMIE_BNA(float, __nv_bfloat16);
-  else LLMIE_BNA(float, float);
+  if (y_bf16 && act_bf16) { LLMIE_BNA(__nv_bfloat16, __nv_bfloat16); }
+  else if (y_bf16) { LLMIE_BNA(__nv_bfloat16, float); }
+  else if (act_bf16) { LLMIE_BNA(float, __nv_bfloat16); }
+  else { LLMIE_BNA(float, float); }
 #undef LLMIE_BNA
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
@@ -251,12 +404,17 @@ extern "C" int llmie_bias_act(const void* u, int u_dtype, const float* bias, voi
   if (n_tokens < 0 || n <= 0 || act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
   if (n_tokens == 0) return LLMIE_OK;
   const size_t total = (size_t)n_tokens * n;
-  const dim3 grid(flat_blocks(total)), block(256);
-#define LLMIE_BA(T, O) launch_k(bias_act_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n, total, act)
-  if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_F32) LLMIE_BA(float, float);
-  else if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_BF16) LLMIE_BA(float, __nv_bfloat16);
-  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_BF16) LLMIE_BA(__nv_bfloat16, __nv_bfloat16);
-  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_F32) LLMIE_BA(__nv_bfloat16, float);
+  const bool vec = n % 8 == 0 && aligned16(u) && aligned16(out) && (!bias || aligned16(bias));
+  const int col_blocks = (n / 8 + 127) / 128;
+  const dim3 grid(vec ? col_blocks : flat_blocks(total), vec ? (n_tokens < 2048 ? n_tokens : 2048) : 1);
+  const dim3 block(vec ? 128 : 256);
+#define LLMIE_BA(T, O)                                                                                             \
+  if (vec) launch_k(bias_act_vec_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n / 8, n_tokens, act); \
+  else launch_k(bias_act_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n, total, act)
+  if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_F32) { LLMIE_BA(float, float); }
+  else if (u_dtype == LLMIE_F32 && out_dtype == LLMIE_BF16) { LLMIE_BA(float, __nv_bfloat16); }
+  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_BF16) { LLMIE_BA(__nv_bfloat16, __nv_bfloat16); }
+  else if (u_dtype == LLMIE_BF16 && out_dtype == LLMIE_F32) { LLMIE_BA(__nv_bfloat16, float); }
   else return LLMIE_ERR_DTYPE;
 #undef LLMIE_BA
   LLMIE_LAUNCH_CHECK();
@@ -303,6 +461,26 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
   if (write_kv && (!k_cache || !v_cache)) return LLMIE_ERR_BAD_ARG;
   if (n_tokens == 0) return LLMIE_OK;
   const dim3 grid(n_tokens), block(row_threads(n_q * hd));
+  // 16-byte accesses: every run of 8 elements (32 bytes of float32, two accesses of 16) starts on 16 bytes
+  const bool vec = hd % 8 == 0 && hdv % 8 == 0 && ld % 8 == 0 && (!v_first || v_first_ld % 8 == 0) && aligned16(proj) &&
+                   aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache) && aligned16(v_first) &&
+                   aligned16(q_w) && aligned16(k_w);
+  if (vec) {
+    const dim3 vblock(row_threads((n_q * hd + 7) / 8));
+    if (dtype == LLMIE_F32)
+      launch_k(qk_norm_store_vec_kernel<float>, grid, vblock, 0, stream, (const float*)proj, ld, (float*)q_out,
+               (float*)k_cache, (float*)v_cache, q_w, k_w, eps, lam_ptr, (const float*)v_first, v_first_ld, tok_pos,
+               tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, write_kv);
+    else if (dtype == LLMIE_BF16)
+      launch_k(qk_norm_store_vec_kernel<__nv_bfloat16>, grid, vblock, 0, stream, (const __nv_bfloat16*)proj, ld,
+               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_w, k_w, eps, lam_ptr,
+               (const __nv_bfloat16*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+               page_size, n_q, n_kv, hd, hdv, write_kv);
+    else
+      return LLMIE_ERR_DTYPE;
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   if (dtype == LLMIE_F32)
     launch_k(qk_norm_store_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, (float*)q_out,
              (float*)k_cache, (float*)v_cache, q_w, k_w, eps, lam_ptr, (const float*)v_first, v_first_ld, tok_pos,

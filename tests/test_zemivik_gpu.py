@@ -89,15 +89,16 @@ def test_embedding_stage_part(dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("y_dtype", ["float32", "bfloat16"])
-def test_norm_on_a_branch_output(dtype, y_dtype):
-    norm, w = build("norm", "rmsnorm", {"size": 200, "eps": 1e-4, "weight_name": ""}, dtype, seed=6)
+@pytest.mark.parametrize("size", [200, 204, 2048])           # 16-byte accesses, element by element, a wide row
+def test_norm_on_a_branch_output(dtype, y_dtype, size):
+    norm, w = build("norm", "rmsnorm", {"size": size, "eps": 1e-4, "weight_name": ""}, dtype, seed=6)
     assert list(w) == [""]
     g = torch.Generator().manual_seed(7)
-    h, y, bias = torch.randn(9, 200, generator=g), torch.randn(9, 200, generator=g) * 5, torch.randn(200, generator=g)
+    h, y, bias = torch.randn(9, size, generator=g), torch.randn(9, size, generator=g) * 5, torch.randn(size, generator=g)
     y = y.to(DTYPES[y_dtype])
     for b in (None, bias):
         hd = h.clone().to(DEV)
-        act = torch.empty(9, 200, dtype=DTYPES[dtype], device=DEV)
+        act = torch.empty(9, size, dtype=DTYPES[dtype], device=DEV)
         norm.add_normed(hd, y.to(DEV), None if b is None else b.to(DEV), act)
         want = h + plain.rms_norm(y.float() + (0 if b is None else b), w[""], 1e-4)
         assert float((hd.cpu() - want).abs().max()) < 2e-5
@@ -105,12 +106,16 @@ def test_norm_on_a_branch_output(dtype, y_dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("activation", ["relu2", "relu", "gelu_tanh", "silu"])
-def test_dense_mlp_part(dtype, activation):
-    ff, w = build("feed_forward", "dense_mlp", {"hidden": 72, "intermediate": 100, "activation": activation}, dtype, seed=8)
+@pytest.mark.parametrize("activation,inner", [("relu2", 100), ("relu2", 128), ("relu", 104), ("gelu_tanh", 100), ("silu", 96)])
+def test_dense_mlp_part(dtype, activation, inner):
+    """Widths that take the one-kernel product with bias and activation (one-token steps of a bfloat16 engine), the
+    16-byte kernels and the element-by-element ones."""
+    ff, w = build("feed_forward", "dense_mlp", {"hidden": 96 if inner == 128 else 72, "intermediate": inner,
+                                                "activation": activation}, dtype, seed=8)
+    hidden = ff.hidden
     g = torch.Generator().manual_seed(9)
     for rows in (3, 40):
-        x = torch.randn(rows, 72, generator=g).to(DTYPES[dtype])
+        x = torch.randn(rows, hidden, generator=g).to(DTYPES[dtype])
         z = x.float() @ w["up"].T + w["up.b"]
         a = {"relu2": torch.relu(z) ** 2, "relu": torch.relu(z), "silu": z * torch.sigmoid(z),
              "gelu_tanh": 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))}[activation]
@@ -121,16 +126,17 @@ def test_dense_mlp_part(dtype, activation):
         bare = ff.forward(x.to(DEV), make_ctx([rows], [0], [0], dtype), defer_bias=True)
         assert float((bare.cpu() + w["down.b"] - got.cpu()).abs().max()) < 1e-5
     if activation == "relu2":
-        same, _ = build("feed_forward", "dense_mlp", {"hidden": 72, "intermediate": 100}, dtype, seed=8)   # the default
+        same, _ = build("feed_forward", "dense_mlp", {"hidden": hidden, "intermediate": inner}, dtype, seed=8)   # the default
         assert same.activation == ff.activation
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("blend", [False, True])
-def test_query_key_norm_blend_and_cache_write(dtype, blend):
+@pytest.mark.parametrize("shape,extra", [((6, 2, 20, 12), 9), ((4, 2, 64, 32), 8), ((5, 5, 16, 40), 16)])
+def test_query_key_norm_blend_and_cache_write(dtype, blend, shape, extra):
     from llm_infer_engine_b200.cache import Cache, KVRequest
     from llm_infer_engine_b200.kernels import ops
-    n_q, n_kv, hd, hdv = 6, 2, 20, 12
+    n_q, n_kv, hd, hdv = shape
     cache = Cache([[KVRequest(n_kv, hd, v_head_dim=hdv)]], 3, 64 * 6, 512, DTYPES[dtype], DEV)
     slots = [cache.take_slot() for _ in range(2)]
     lens, starts = [70, 3], [0, 0]
@@ -138,9 +144,9 @@ def test_query_key_norm_blend_and_cache_write(dtype, blend):
         cache.reserve(s, l)
     ctx = make_ctx(lens, starts, slots, dtype)
     g = torch.Generator().manual_seed(10)
-    T, width = sum(lens), n_q * hd + n_kv * hd + n_kv * hdv + 9                    # nine more columns follow v
+    T, width = sum(lens), n_q * hd + n_kv * hd + n_kv * hdv + extra               # more columns follow v
     proj = (torch.randn(T, width, generator=g) * 3).to(DTYPES[dtype])
-    first = torch.randn(T, n_kv * hdv + 5, generator=g).to(DTYPES[dtype])
+    first = torch.randn(T, n_kv * hdv + (5 if extra == 9 else 8), generator=g).to(DTYPES[dtype])
     qw, kw = torch.rand(n_q * hd, generator=g) + 0.5, torch.rand(n_kv * hd, generator=g) + 0.5
     lam = torch.tensor([0.3])
     kv = cache.unit(0).kv
