@@ -152,7 +152,22 @@ __global__ void bias_act_vec_kernel(const T* __restrict__ u, const float* __rest
 #pragma unroll
   for (int e = 0; e < 8; ++e) b[e] = 0.f;
   if (bias) load8(bias + (size_t)j8 * 8, b);
-  for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+  // two rows at a time: both loads are on their way before either is used
+  int t = blockIdx.y;
+  for (; t + (int)gridDim.y < n_tokens; t += 2 * gridDim.y) {
+    const size_t o0 = ((size_t)t * n8 + j8) * 8, o1 = ((size_t)(t + gridDim.y) * n8 + j8) * 8;
+    float z0[8], z1[8];
+    load8(u + o0, z0);
+    load8(u + o1, z1);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      z0[e] = apply_act(z0[e] + b[e], act);
+      z1[e] = apply_act(z1[e] + b[e], act);
+    }
+    store8(out + o0, z0);
+    store8(out + o1, z1);
+  }
+  if (t < n_tokens) {
     float z[8];
     load8(u + ((size_t)t * n8 + j8) * 8, z);
 #pragma unroll
@@ -260,39 +275,61 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
                                          int n_kv, int hd, int hdv, int write_kv) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red[32];
+  __shared__ float red[2][32];
   const int t = blockIdx.x;
   const int nq = n_q * hd, nk = n_kv * hd, nv = n_kv * hdv;
   const T* qs = proj + (size_t)t * ld;
   const T* ks = qs + nq;
   const T* vs = ks + nk;
-  float rq = 1.f, rk = 1.f;
+  // The first run of 8 query elements of a thread stays in registers between the sum and the store (with one
+  // thread per run, the usual case, q is read once); both sums of squares go through one block reduction.
+  const int i0 = threadIdx.x * 8;
+  float q0[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) q0[e] = 0.f;
+  if (i0 < nq) load8(qs + i0, q0);
+  float sq = 0.f, sk = 0.f;
   if (q_w) {
-    float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < nq; i += blockDim.x * 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sq += q0[e] * q0[e];
+    for (int i = i0 + blockDim.x * 8; i < nq; i += blockDim.x * 8) {
       float x[8];
       load8(qs + i, x);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+      for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
     }
-    ss = block_sum(ss, red);
-    rq = 1.f / sqrtf(ss / (float)nq + eps);
   }
   if (k_w && write_kv) {
-    float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < nk; i += blockDim.x * 8) {
+    for (int i = i0; i < nk; i += blockDim.x * 8) {
       float x[8];
       load8(ks + i, x);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+      for (int e = 0; e < 8; ++e) sk += x[e] * x[e];
     }
-    ss = block_sum(ss, red);
-    rk = 1.f / sqrtf(ss / (float)nk + eps);
   }
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) {
+      red[0][warp] = sq;
+      red[1][warp] = sk;
+    }
+    __syncthreads();
+    sq = warp_sum(lane < n_warps ? red[0][lane] : 0.f);
+    sk = warp_sum(lane < n_warps ? red[1][lane] : 0.f);
+  }
+  const float rq = q_w ? 1.f / sqrtf(sq / (float)nq + eps) : 1.f;
+  const float rk = (k_w && write_kv) ? 1.f / sqrtf(sk / (float)nk + eps) : 1.f;
   T* qo = q_out + (size_t)t * nq;
-  for (int i = threadIdx.x * 8; i < nq; i += blockDim.x * 8) {
+  for (int i = i0; i < nq; i += blockDim.x * 8) {
     float x[8];
-    load8(qs + i, x);
+    if (i == i0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = q0[e];
+    } else {
+      load8(qs + i, x);
+    }
     if (q_w) {
       float w8[8];
       load8(q_w + i, w8);
@@ -328,7 +365,7 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
       float f[8];
       load8(vf + i, f);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = to_f32(from_f32<T>((1.f - lam) * x[e] + lam * f[e]));
+      for (int e = 0; e < 8; ++e) x[e] = (1.f - lam) * x[e] + lam * f[e];
     }
     store8(v_cache + (((size_t)page * n_kv + hk) * page_size + in_page) * hdv + e0, x);
   }
@@ -405,9 +442,12 @@ extern "C" int llmie_bias_act(const void* u, int u_dtype, const float* bias, voi
   if (n_tokens == 0) return LLMIE_OK;
   const size_t total = (size_t)n_tokens * n;
   const bool vec = n % 8 == 0 && aligned16(u) && aligned16(out) && (!bias || aligned16(bias));
-  const int col_blocks = (n / 8 + 127) / 128;
-  const dim3 grid(vec ? col_blocks : flat_blocks(total), vec ? (n_tokens < 2048 ? n_tokens : 2048) : 1);
-  const dim3 block(vec ? 128 : 256);
+  const int vthreads = n / 8 >= 256 ? 256 : ((n / 8 + 31) / 32) * 32;
+  const int col_blocks = vec ? (n / 8 + vthreads - 1) / vthreads : 1;
+  int row_blocks = (148 * 16 + col_blocks - 1) / col_blocks;        // a few thousand blocks, several rows a thread
+  row_blocks = row_blocks < n_tokens ? row_blocks : n_tokens;
+  const dim3 grid(vec ? col_blocks : flat_blocks(total), vec ? row_blocks : 1);
+  const dim3 block(vec ? vthreads : 256);
 #define LLMIE_BA(T, O)                                                                                             \
   if (vec) launch_k(bias_act_vec_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n / 8, n_tokens, act); \
   else launch_k(bias_act_kernel<T, O>, grid, block, 0, stream, (const T*)u, bias, (O*)out, n, total, act)
