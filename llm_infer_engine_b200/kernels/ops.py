@@ -426,13 +426,9 @@ def qk_norm_store(proj, q_out, k_cache, v_cache, q_w, k_w, eps: float, tok_pos, 
 
 
 def attention_decode_supported(head_dim: int, dtype: torch.dtype) -> bool:
-    code = _DT.get(dtype)
-    if code is None:
-        return False
-    lib = build.load("attention_decode")
-    lib.llmie_attention_decode_supported.argtypes = [_c_int, _c_int]
-    lib.llmie_attention_decode_supported.restype = _c_int
-    return bool(lib.llmie_attention_decode_supported(head_dim, code))
+    """The head sizes attention_decode.cu is instantiated for. Answered here, without loading the library: a model
+    whose sizes it does not take never has it compiled."""
+    return dtype in _DT and head_dim in (16, 32, 64, 128)
 
 
 def attention_decode_run_len(n_seqs: int, head_dim: int, dtype: torch.dtype) -> int:
@@ -512,10 +508,8 @@ MMA_MAX_BLOCKS = 148 * 2        # blocks the decode attention aims at: two per S
 
 
 def attention_decode_mma_supported(head_dim: int, dtype: torch.dtype, page_size: int) -> bool:
-    if dtype != torch.bfloat16:
-        return False
-    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_supported", [_c_int] * 3, query=True)
-    return bool(f(head_dim, _DT[dtype], page_size))
+    """The sizes attention_decode_mma.cu is instantiated for (answered without loading the library)."""
+    return dtype == torch.bfloat16 and page_size == 64 and head_dim in (64, 128)
 
 
 def attention_decode_mma_pages(n_seqs: int, n_q: int, n_kv: int, max_kv_len: int,
