@@ -6,6 +6,12 @@
 //   variant "gate":  x = rmsnorm(h) ; act = silu(x Wg^T) * (x Wu^T)
 //   variant "f32":   x = rmsnorm(h) ; out = x W^T in float32 (the LM head after the final norm)
 //
+// For layers whose norm sits on a branch's OUTPUT (h += norm(y)) the same kernel has a second way of making x: the
+// add that closes the previous branch is folded into the product that opens the next one,
+//   x = h + (y + bias) * rsqrt(mean((y + bias)^2) + eps) * w      (float32; block 0 also writes it out as the new stream)
+//   variant "store":    out = x W^T in bfloat16
+//   variant "bias_act": out = act(x W^T + b) in bfloat16
+//
 // In the reference these are 5, 5 and 2 launches (src/model.py:114,54,62,69-74; :127,23; :183).
 // In a one-token step every launch costs a few microseconds of latency whatever it computes,
 // and the layer is a chain of dependent launches, so fewer launches is what shortens it.
@@ -25,7 +31,17 @@ namespace llmie {
 constexpr int kFdUnroll = 4;
 constexpr int kFdPad = 32;          // bfloat16 elements of padding per staged row: 16-byte reads do not collide
 
-enum FusedVariant { kVarQkvRope = 0, kVarGateSwiGLU = 1, kVarF32 = 2 };
+enum FusedVariant { kVarQkvRope = 0, kVarGateSwiGLU = 1, kVarF32 = 2, kVarStoreBf16 = 3, kVarBiasAct = 4 };
+
+// The branch output that is normalised and added to the stream while x is staged (BRANCH instances only), and the
+// bias and activation of the "bias_act" epilogue.
+struct BranchArgs {
+  const float* y;          // [batch, K] the previous branch's output
+  const float* y_bias;     // [K] or null
+  float* h_out;            // [batch, K] the new stream (not the buffer that is read)
+  const float* out_bias;   // [N] or null
+  int act;
+};
 
 struct RopeStoreArgs {
   __nv_bfloat16* q_out;          // [batch, n_q * hd]
@@ -119,7 +135,7 @@ __device__ __forceinline__ void rope_ahead(RopeAhead& ra, int tile, int tiles, i
 template <int VAR>
 __device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int tile, int lo, int hi, int g, int t, float rs0,
                                               float rs1, int batch, void* out, int ldo, const RopeStoreArgs& rope,
-                                              const RopeAhead& ra) {
+                                              const RopeAhead& ra, const BranchArgs& br) {
 #pragma unroll
   for (int cc = 0; cc < 2; ++cc) {
     const int b = 2 * t + cc;
@@ -130,6 +146,14 @@ __device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int tile, i
       float* o = reinterpret_cast<float*>(out) + (size_t)b * ldo;
       o[lo + g] = x1;
       o[hi + g] = x2;
+    } else if (VAR == kVarStoreBf16 || VAR == kVarBiasAct) {
+      if (VAR == kVarBiasAct) {
+        x1 = apply_act(br.out_bias ? x1 + br.out_bias[lo + g] : x1, br.act);
+        x2 = apply_act(br.out_bias ? x2 + br.out_bias[hi + g] : x2, br.act);
+      }
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)b * ldo;
+      o[lo + g] = __float2bfloat16_rn(x1);
+      o[hi + g] = __float2bfloat16_rn(x2);
     } else if (VAR == kVarGateSwiGLU) {
       const float act = x1 / (1.f + expf(-x1)) * x2;
       reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + g] = __float2bfloat16_rn(act);
@@ -176,11 +200,11 @@ __device__ __forceinline__ void fd_team_sync(int team, int threads) {
 // tile; no block-wide barrier), whose lanes hold whole (row, row + 8) x (column pair) results: the
 // rotation pairs, the gate and up rows, or plain outputs. With S = 1 (many tiles: the LM head) a
 // warp streams whole rows and nothing is exchanged at all.
-template <int VAR, int WARPS>
+template <int VAR, int WARPS, bool BRANCH>
 __global__ void __launch_bounds__(WARPS * 32)
 norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, float eps,
                  const __nv_bfloat16* __restrict__ W, void* __restrict__ out, int batch, int K, int ldo, int tiles,
-                 int half_n, int S, RopeStoreArgs rope) {
+                 int half_n, int S, RopeStoreArgs rope, BranchArgs br) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char fd_smem[];
   const int xs_stride = K + kFdPad;                                        // elements
@@ -237,6 +261,73 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
   if (j == 0) rope_ahead<VAR>(ra, team * gridDim.x + blockIdx.x, tiles, t, g, batch, half_n, rope);
   pdl_wait();              // h is the previous kernels' result
 
+  float rs0, rs1;                     // rstd of the two batch columns this lane holds results of
+  if (BRANCH) {
+    // ---- the previous branch closes here: sums of squares of y + bias per row, then x = h + (y + bias) rstd w as
+    // bfloat16 rows in shared memory (block 0 also writes x, in float32, as the new stream)
+    float ssq[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) ssq[b] = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += WARPS * 32 * 8) {
+      float bv[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) bv[e] = 0.f;
+      if (br.y_bias) load8(br.y_bias + k, bv);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (b < batch) {
+          float yv[8];
+          load8(br.y + (size_t)b * K + k, yv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ssq[b] = fmaf(yv[e] + bv[e], yv[e] + bv[e], ssq[b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const float sq = warp_sum(ssq[b]);
+      if (lane == 0) ssw[warp * 8 + b] = sq;
+    }
+    __syncthreads();
+    float rstd[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      float s_ = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) s_ += ssw[w * 8 + b];
+      rstd[b] = 1.f / sqrtf(s_ / (float)K + eps);
+    }
+    for (int k = threadIdx.x * 8; k < K; k += WARPS * 32 * 8) {
+      float wv[8], bv[8];
+      load8(norm_w + k, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) bv[e] = 0.f;
+      if (br.y_bias) load8(br.y_bias + k, bv);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        float xv[8];
+        if (b < batch) {
+          float yv[8];
+          load8(h + (size_t)b * K + k, xv);
+          load8(br.y + (size_t)b * K + k, yv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xv[e] += (yv[e] + bv[e]) * rstd[b] * wv[e];
+          if (blockIdx.x == 0) store8(br.h_out + (size_t)b * K + k, xv);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xv[e] = 0.f;
+        }
+        uint4 packed;
+        packed.x = fd_pack(xv[0], xv[1]);
+        packed.y = fd_pack(xv[2], xv[3]);
+        packed.z = fd_pack(xv[4], xv[5]);
+        packed.w = fd_pack(xv[6], xv[7]);
+        *reinterpret_cast<uint4*>(xs + (size_t)b * xs_stride + k) = packed;
+      }
+    }
+    __syncthreads();
+    rs0 = rs1 = 1.f;
+  } else {
   // ---- h * w as bfloat16 rows in shared memory, and the sum of squares of every row
   {
     float ssq[8];
@@ -271,7 +362,6 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
     }
     __syncthreads();
   }
-  float rs0, rs1;                     // rstd of the two batch columns this lane holds results of
   {
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -281,6 +371,7 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
     }
     rs0 = rsqrtf(s0 / (float)K + eps);
     rs1 = rsqrtf(s1 / (float)K + eps);
+  }
   }
   const uint4* x_row = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride) + t;   // this lane's batch row
 
@@ -317,7 +408,7 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
       if (j == 0) {                                                                  \
         int lo, hi;                                                                  \
         tile_rows<VAR>(tile, hd, half_n, lo, hi);                                    \
-        tile_epilogue<VAR>(acc, tile, lo, hi, g, t, rs0, rs1, batch, out, ldo, rope, ra); \
+        tile_epilogue<VAR>(acc, tile, lo, hi, g, t, rs0, rs1, batch, out, ldo, rope, ra, br); \
       }                                                                              \
       acc[0] = acc[1] = acc[2] = acc[3] = 0.f;                                       \
       cr = 0;                                                                        \
@@ -342,7 +433,7 @@ static size_t fused_smem(int K) {
 }
 
 // Blocks of this instance that one SM holds at once (0 if it cannot run at all with this K).
-template <int VAR, int WARPS>
+template <int VAR, int WARPS, bool BRANCH = false>
 static int fused_blocks_per_sm(int K) {
   static int cached_k = -1, cached = 0;
   if (cached_k != K) {
@@ -350,8 +441,8 @@ static int fused_blocks_per_sm(int K) {
     int n = 0;
     if (smem <= 200 * 1024) {
       if (smem > 48 * 1024)
-        cudaFuncSetAttribute(norm_gemm_kernel<VAR, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_gemm_kernel<VAR, WARPS>, WARPS * 32, smem) != cudaSuccess)
+        cudaFuncSetAttribute(norm_gemm_kernel<VAR, WARPS, BRANCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_gemm_kernel<VAR, WARPS, BRANCH>, WARPS * 32, smem) != cudaSuccess)
         n = 0;
     }
     cached = n;
@@ -366,10 +457,11 @@ constexpr int kFdWarps = 8;
 // loads are requested while the first is finished, which hides the tile's end; measured on the gate / up
 // product of the 1B shape: 4 warps a tile and 1.7 tiles a team beat 2 warps and one tile by 1.7 % of the
 // whole step); few tiles make few blocks, spread over the SMs.
-template <int VAR>
+template <int VAR, bool BRANCH = false>
 static int launch_fused_w(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
-                          int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
-  const int per_sm = fused_blocks_per_sm<VAR, kFdWarps>(K);
+                          int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream,
+                          const BranchArgs& br = BranchArgs{}) {
+  const int per_sm = fused_blocks_per_sm<VAR, kFdWarps, BRANCH>(K);
   if (per_sm < 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
   const long long resident_warps = 148LL * per_sm * kFdWarps;
   int S = kFdWarps;
@@ -377,8 +469,8 @@ static int launch_fused_w(const float* h, const float* norm_w, float eps, const 
   const int teams_per_block = kFdWarps / S;
   int blocks = (tiles + teams_per_block - 1) / teams_per_block;
   if (blocks > 148 * per_sm) blocks = 148 * per_sm;
-  launch_k(norm_gemm_kernel<VAR, kFdWarps>, dim3(blocks), dim3(kFdWarps * 32), fused_smem<VAR, kFdWarps>(K), stream, h,
-           norm_w, eps, (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, S, rope);
+  launch_k(norm_gemm_kernel<VAR, kFdWarps, BRANCH>, dim3(blocks), dim3(kFdWarps * 32), fused_smem<VAR, kFdWarps>(K),
+           stream, h, norm_w, eps, (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, S, rope, br);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -453,4 +545,25 @@ extern "C" int llmie_norm_qkv_rope(const float* h, const float* norm_w, float ep
   r.write_kv = write_kv;
   const int tiles = (n_q + 2 * n_kv) * (hd / 16);
   return launch_fused_w<kVarQkvRope>(h, norm_w, eps, W, nullptr, batch, K, 0, tiles, 0, r, stream);
+}
+
+// The add that closes a branch folded into the product that opens the next one (layers with the norm on the branch's
+// output): x = h + (y + y_bias) * rsqrt(mean((y + y_bias)^2) + eps) * norm_w in float32, written to h_out (a buffer
+// other than h), and out[batch, N] bfloat16 = x W^T, or act(x W^T + out_bias) with with_act (act a code of apply_act;
+// out_bias float32 [N] or null). y, h, h_out float32 [batch, K]; y_bias float32 [K] or null.
+extern "C" int llmie_branch_norm_gemm(const float* h, const float* y, const float* y_bias, const float* norm_w, float eps,
+                                      float* h_out, const void* W, void* out, const float* out_bias, int act,
+                                      int with_act, int batch, int N, int K, cudaStream_t stream) {
+  int rc = check_common(h, norm_w, W, batch, N, K);
+  if (rc != LLMIE_OK) return rc;
+  if (!y || !h_out || h_out == h || act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(y) || !aligned16(h_out) || !aligned16(y_bias)) return LLMIE_ERR_ALIGNMENT;
+  if (N % 16) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (batch == 0) return LLMIE_OK;
+  RopeStoreArgs none = {};
+  none.hd = 16;
+  const BranchArgs br = {y, y_bias, h_out, out_bias, act};
+  if (with_act)
+    return launch_fused_w<kVarBiasAct, true>(h, norm_w, eps, W, out, batch, K, N, N / 16, 0, none, stream, br);
+  return launch_fused_w<kVarStoreBf16, true>(h, norm_w, eps, W, out, batch, K, N, N / 16, 0, none, stream, br);
 }

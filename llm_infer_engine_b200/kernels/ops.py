@@ -715,6 +715,33 @@ def norm_gate_swiglu(h, norm_w, eps: float, w_gate_up, act):
     return act
 
 
+def branch_norm_gemm(h, y, y_bias, norm_w, eps: float, h_out, w, out, out_bias=None, act: Optional[int] = None):
+    """The add that closes a branch, folded into the product that opens the next one (one-token steps of layers
+    whose norm sits on the branch's output): h_out = h + rmsnorm(y + y_bias) * norm_w in float32 (h_out must not be
+    h), and out (bfloat16 [batch, N]) = h_out w^T, or act(h_out w^T + out_bias) when `act` is an ACT_* code.
+    h, y, h_out float32 [batch <= 8, K]; y_bias float32 [K] or None; out_bias float32 [N] or None."""
+    batch, K = _norm_gemm_common(h, norm_w, w, "branch_norm_gemm")
+    N = w.shape[0]
+    _need(y, "y", torch.float32, (batch, K))
+    _need(h_out, "h_out", torch.float32, (batch, K))
+    _need(out, "out", torch.bfloat16, (batch, N))
+    if h_out.data_ptr() == h.data_ptr():
+        raise KernelError("branch_norm_gemm: h_out must be another buffer than h")
+    if y_bias is not None:
+        _need(y_bias, "y_bias", torch.float32, (K,))
+    if out_bias is not None:
+        _need(out_bias, "out_bias", torch.float32, (N,))
+    if N % 16:
+        raise KernelError("branch_norm_gemm: N must be a multiple of 16")
+    _work(_nbytes(h, y, h_out, w, out), 2.0 * batch * N * K)
+    f = _fn("gemm_fused_decode", "llmie_branch_norm_gemm",
+            [_c_void_p] * 4 + [_c_float] + [_c_void_p] * 4 + [_c_int] * 5 + [_c_void_p])
+    _check(f(h.data_ptr(), y.data_ptr(), _ptr(y_bias), norm_w.data_ptr(), float(eps), h_out.data_ptr(), w.data_ptr(),
+             out.data_ptr(), _ptr(out_bias), int(act or 0), 0 if act is None else 1, batch, N, K, _stream()),
+           "branch_norm_gemm")
+    return out
+
+
 def norm_gemm_f32(h, norm_w, eps: float, w, out):
     """out[batch, N] float32 = (rmsnorm(h) * norm_w) w^T in one kernel (final norm + LM head)."""
     batch, K = _norm_gemm_common(h, norm_w, w, "norm_gemm_f32")

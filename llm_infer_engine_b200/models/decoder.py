@@ -15,7 +15,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops, trace
-from ..parts.base import Block, ParamSpec, Part, Runtime, build_part, lookup
+from ..parts.base import Block, DeferredBranchAdd, ParamSpec, Part, Runtime, build_part, lookup
 from ..parts.linear import Linear
 
 
@@ -114,10 +114,14 @@ class DecoderModel:
             unit = cache.unit(self.unit_of_entry[pos])
             ctx.entry = pos
             block = self.blocks[call.layer]
+            if isinstance(pending, DeferredBranchAdd) and not getattr(block, "accepts_deferred_branch_add", False):
+                h, pending = pending.apply(), None      # this block does not know deferred adds: done here
             h, pending = block.forward(h, pending, ctx, unit, call.cache_of is None)
             if not getattr(block, "leaves_rounded_stream", False):
                 ctx.carry.pop("h_act", None)      # a rounded copy of the stream from before this block is stale
         trace.pop()
+        if isinstance(pending, DeferredBranchAdd):
+            h, pending = pending.apply(), None          # the last layer's add
         ctx.carry.clear()
         trace.push("Output")
         logits = None

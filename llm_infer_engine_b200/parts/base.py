@@ -115,6 +115,34 @@ class DeferredNorm:
         return self.norm.forward(self.h, None)
 
 
+class DeferredBranchAdd:
+    """h += norm(y + bias) that has not been done: what a block whose norm sits on the branch's OUTPUT hands on instead
+    of doing it, so that the product that opens the next branch can do it while it stages its input. Whoever receives
+    one (a part that declares `accepts_deferred_branch_add`, the next block, or the model after the last layer)
+    either folds it into its first kernel and sets `resolved` to the new stream, or calls `apply()`."""
+
+    def __init__(self, norm: Norm, h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor]):
+        self.norm, self.h, self.y, self.bias = norm, h, y, bias
+        self.resolved: Optional[torch.Tensor] = None       # the stream after the add, once someone has done it
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def foldable(self, weight: torch.Tensor) -> bool:
+        """Whether a product with this bfloat16 weight can do the add itself (one-token steps of up to 8 rows)."""
+        from ..kernels import ops
+        return (getattr(self.norm, "kind", None) == "rmsnorm" and weight.dtype == torch.bfloat16
+                and self.y.dtype == torch.float32 and weight.shape[0] % 16 == 0
+                and ops.norm_gemm_supported(self.h.shape[0], self.h.shape[1]))
+
+    def apply(self, act: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Does the add in a kernel of its own; `act` receives the new stream rounded to its dtype."""
+        if self.resolved is None:
+            self.resolved = self.norm.add_normed(self.h, self.y, self.bias, act)
+        return self.resolved
+
+
 class PositionEncoding(Part):
     def encode_and_store(self, qkv: torch.Tensor, ctx, kv, n_q: int, n_kv: int, head_dim: int,
                          write_kv: bool) -> torch.Tensor:
@@ -136,6 +164,7 @@ class Mixer(Part):
     """
     accepts_deferred_norm = False
     adds_to_residual = False
+    accepts_deferred_branch_add = False     # x may be a DeferredBranchAdd: the part folds it or calls x.apply(act)
 
     def cache_requests(self) -> List[object]:
         """KVRequest / StateRequest objects: what one run of this mixer needs per sequence."""

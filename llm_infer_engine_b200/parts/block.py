@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops, trace
-from .base import Block, call_branch, register_block
+from .base import Block, DeferredBranchAdd, call_branch, register_block
 
 
 class PreNormBlock(Block):
@@ -47,9 +47,12 @@ class BranchNormBlock(Block):
     sits on each branch's OUTPUT. The sum stays float32; a bfloat16 engine's products read the stream rounded to
     bfloat16, and that rounded copy is written by the same kernel that adds the branch (it travels to the next
     layer in `ctx.carry["h_act"]`). A feed-forward that declares `down_bias` has it added inside the norm's
-    kernel."""
+    kernel. In one-token steps of up to 8 rows of a bfloat16 engine the add is not done here at all: it is handed
+    on as a `DeferredBranchAdd` to the part that opens the next branch (the feed-forward, or the next layer's
+    mixer, which gets it as `pending`), whose first product does it while it stages its input."""
     ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
     leaves_rounded_stream = True
+    accepts_deferred_branch_add = True
 
     def _rounded(self, h, ctx):
         """The stream as the products read it: itself in a float32 engine, else its bfloat16 copy."""
@@ -64,35 +67,55 @@ class BranchNormBlock(Block):
         return None if self.runtime.dtype == torch.float32 else torch.empty(h.shape, dtype=self.runtime.dtype,
                                                                             device=h.device)
 
-    def _mixer_branch(self, h, pending, ctx, unit, owns_cache):
+    def _defers(self, h, ctx) -> bool:
+        """Whether the adds of this step are handed on instead of done: one-token steps the fused product takes."""
+        return self.runtime.dtype == torch.bfloat16 and ctx.decode and ops.norm_gemm_supported(h.shape[0], h.shape[1])
+
+    def _close(self, h, y, bias, norm, ctx, nxt):
+        """Ends a branch: h += norm(y + bias), here, or handed to `nxt` (the part that opens the next branch, None =
+        unknown) when it can fold the add into its first product. Returns (h, x for the next branch, pending)."""
+        if self._defers(h, ctx) and y.dtype == torch.float32 and (nxt is None or getattr(nxt, "accepts_deferred_branch_add", False)):
+            d = DeferredBranchAdd(norm, h, y, bias)
+            return h, d, d
+        act = self._new_rounded(h)
+        norm.add_normed(h, y, bias, act)
+        return h, (h if act is None else act), None
+
+    def _open(self, h, pending, ctx):
+        """What the mixer reads: the deferred add of the layer before, or the (rounded) stream."""
+        if isinstance(pending, DeferredBranchAdd):
+            if self.mixer.accepts_deferred_branch_add:
+                return pending
+            h = pending.apply()
+            pending = None
         if pending is not None:
             ops.residual_add(h, pending)
             ctx.carry.pop("h_act", None)
-        x = self._rounded(h, ctx)
-        y = call_branch(self.mixer, x, ctx, unit, owns_cache)
-        act = self._new_rounded(h)
-        self.mixer_norm.add_normed(h, y, None, act)
-        return act
+        return self._rounded(h, ctx)
 
     def forward(self, h, pending, ctx, unit, owns_cache):
         tracing = trace.active()
         if tracing:
             trace.push(f"Attn_{ctx.entry}")
-        act = self._mixer_branch(h, pending, ctx, unit, owns_cache)
+        x = self._open(h, pending, ctx)
+        y = call_branch(self.mixer, x, ctx, unit, owns_cache)
+        if isinstance(x, DeferredBranchAdd):
+            h = x.apply()                      # the new stream (the mixer's first product has made it)
+        ff = self.feed_forward
+        h, x, _ = self._close(h, y, None, self.mixer_norm, ctx, ff)
         if tracing:
             trace.pop()
             trace.push(f"FFN_{ctx.entry}")
-        ff = self.feed_forward
         deferred = getattr(ff, "down_bias", None)
-        x = h if act is None else act
         y = ff.forward(x, ctx, defer_bias=True) if deferred is not None else call_branch(ff, x, ctx)
-        act = self._new_rounded(h)
-        self.feed_forward_norm.add_normed(h, y, deferred, act)
-        if act is not None:
-            ctx.carry["h_act"] = act
+        if isinstance(x, DeferredBranchAdd):
+            h = x.apply()
+        h, x, handed_on = self._close(h, y, deferred, self.feed_forward_norm, ctx, None)
+        if handed_on is None and x is not h:
+            ctx.carry["h_act"] = x
         if tracing:
             trace.pop()
-        return h, None
+        return h, handed_on
 
 
 class BranchNormMixerBlock(BranchNormBlock):
@@ -100,10 +123,14 @@ class BranchNormMixerBlock(BranchNormBlock):
     ROLES = {"mixer": "mixer", "mixer_norm": "norm"}
 
     def forward(self, h, pending, ctx, unit, owns_cache):
-        act = self._mixer_branch(h, pending, ctx, unit, owns_cache)
-        if act is not None:
-            ctx.carry["h_act"] = act
-        return h, None
+        x = self._open(h, pending, ctx)
+        y = call_branch(self.mixer, x, ctx, unit, owns_cache)
+        if isinstance(x, DeferredBranchAdd):
+            h = x.apply()
+        h, x, handed_on = self._close(h, y, None, self.mixer_norm, ctx, None)
+        if handed_on is None and x is not h:
+            ctx.carry["h_act"] = x
+        return h, handed_on
 
 
 register_block("branch_norm", BranchNormBlock)

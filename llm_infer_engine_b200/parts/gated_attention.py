@@ -25,7 +25,7 @@ import torch
 
 from ..cache.cache import KVRequest
 from ..kernels import ops, trace
-from .base import AttentionOptions, Mixer, ParamSpec, register_mixer
+from .base import AttentionOptions, DeferredBranchAdd, Mixer, ParamSpec, register_mixer
 from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm",
@@ -38,6 +38,8 @@ class GatedAttention(Mixer):
     (None, "first": leaves its projected values for later layers, or "blend": mixes them into its own),
     blend_key (name under which the first layer's values travel through the step), names (overrides of the
     tensors' checkpoint sub-names)."""
+
+    accepts_deferred_branch_add = True
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -105,7 +107,11 @@ class GatedAttention(Mixer):
         kv = unit.kv
         T = x.shape[0]
         trace.push("QKV_proj")
-        proj = self.proj(x)                                   # [T, q | k | v | gate]
+        if isinstance(x, DeferredBranchAdd):
+            # one-token steps: the add that closes the previous layer happens inside this product's kernel
+            proj = self.proj.after_branch_add(x) if x.foldable(self.proj.weight) else self.proj(_rounded(x, self.runtime))
+        else:
+            proj = self.proj(x)                               # [T, q | k | v | gate]
         trace.pop()
         v_first = None
         if self.value_blend == "first":
@@ -130,6 +136,15 @@ class GatedAttention(Mixer):
         y = self.o(out, out_dtype=torch.float32)
         trace.pop()
         return y
+
+
+def _rounded(pending: DeferredBranchAdd, runtime) -> torch.Tensor:
+    """Does a deferred branch add in its own kernel and returns the new stream as a product reads it."""
+    if runtime.dtype == torch.float32:
+        return pending.apply()
+    act = torch.empty(pending.shape, dtype=runtime.dtype, device=pending.h.device)
+    pending.apply(act)
+    return act
 
 
 register_mixer("gated_attention", GatedAttention)

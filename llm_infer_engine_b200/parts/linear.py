@@ -70,6 +70,18 @@ class Linear:
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
         return ops.gemm_skinny(x, self.weight, out, ops.SKINNY_SWIGLU)
 
+    def after_branch_add(self, pending, bias: Optional[torch.Tensor] = None, act: Optional[int] = None) -> torch.Tensor:
+        """The product with `pending` (a DeferredBranchAdd) as its input: the add that closes the previous branch
+        happens inside this product's kernel. Returns bfloat16 x W^T, or act(x W^T + bias) when `act` is given; the new
+        stream is left in `pending.resolved`. Only for what `pending.foldable(self.weight)` allows."""
+        h = pending.h
+        h_out = torch.empty_like(h)
+        out = torch.empty((h.shape[0], self.out_features), dtype=torch.bfloat16, device=h.device)
+        ops.branch_norm_gemm(h, pending.y, pending.bias, pending.norm.weight, pending.norm.eps, h_out, self.weight, out,
+                             bias, act)
+        pending.resolved = h_out
+        return out
+
     def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int) -> Optional[torch.Tensor]:
         """act(x W^T + bias) in one kernel (bfloat16, up to SKINNY_BEST_BATCH rows), or None when no kernel for
         this shape exists."""

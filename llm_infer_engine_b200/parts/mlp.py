@@ -8,7 +8,7 @@ from typing import Dict
 import torch
 
 from ..kernels import ops, trace
-from .base import DeferredNorm, FeedForward, ParamSpec, register_feed_forward
+from .base import DeferredBranchAdd, DeferredNorm, FeedForward, ParamSpec, register_feed_forward
 from .linear import Linear
 
 
@@ -78,6 +78,8 @@ class DenseMLP(FeedForward):
     that adds the output bias inside its own next kernel calls `forward(..., defer_bias=True)` and reads
     `down_bias` itself."""
 
+    accepts_deferred_branch_add = True
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
@@ -114,7 +116,16 @@ class DenseMLP(FeedForward):
     def forward(self, x, ctx, residual=None, defer_bias: bool = False):
         trace.push("FFN")
         try:
-            a = self.up.bias_act(x, self.up_bias, self.activation)      # product, bias and activation in one kernel
+            a = None
+            if isinstance(x, DeferredBranchAdd):
+                if x.foldable(self.up.weight):
+                    # one-token steps: the add that closes the mixer's branch, the product, bias and activation
+                    a = self.up.after_branch_add(x, self.up_bias, self.activation)
+                else:
+                    from .gated_attention import _rounded
+                    x = _rounded(x, self.runtime)
+            if a is None:
+                a = self.up.bias_act(x, self.up_bias, self.activation)  # product, bias and activation in one kernel
             if a is None:
                 u = self.up(x)
                 a = torch.empty_like(u)

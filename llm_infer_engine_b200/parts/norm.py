@@ -17,6 +17,8 @@ class RMSNorm(Norm):
     """params: size (width of a row), eps; weight_name (the tensor's name under the part's checkpoint name,
     default "weight"; "" = the part's name itself)."""
 
+    kind = "rmsnorm"
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         self.size = int(params["size"])

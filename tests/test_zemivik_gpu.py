@@ -176,6 +176,31 @@ def test_query_key_norm_blend_and_cache_write(dtype, blend, shape, extra):
         row += l
 
 
+@pytest.mark.parametrize("batch", [1, 5, 8])
+@pytest.mark.parametrize("K,N", [(96, 48), (2048, 160)])
+def test_branch_add_folded_into_the_next_product(batch, K, N):
+    """h_out = h + norm(y + bias) * w and out = h_out W^T (or relu(h_out W^T + b)^2) in one kernel, against the two
+    steps done apart in float64."""
+    from llm_infer_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(batch + K)
+    h, y = torch.randn(batch, K, generator=g) * 2, torch.randn(batch, K, generator=g) * 7
+    y_bias, norm_w = torch.randn(K, generator=g), torch.rand(K, generator=g) + 0.5
+    W = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    out_bias = torch.randn(N, generator=g)
+    for yb in (None, y_bias):
+        want_h = h.double() + plain.rms_norm(y.double() + (0 if yb is None else yb.double()), norm_w.double(), 1e-5)
+        z = want_h.to(torch.bfloat16).double() @ W.double().T
+        for act, want in ((None, z), (ops.ACT_RELU2, torch.relu(z + out_bias.double()) ** 2)):
+            h_dev = h.to(DEV)
+            h_out = torch.empty_like(h_dev)
+            out = torch.empty(batch, N, dtype=torch.bfloat16, device=DEV)
+            ops.branch_norm_gemm(h_dev, y.to(DEV), None if yb is None else yb.to(DEV), norm_w.to(DEV), 1e-5, h_out,
+                                 W.to(DEV), out, out_bias.to(DEV) if act is not None else None, act)
+            assert torch.equal(h_dev.cpu(), h)                                      # the stream that was read is untouched
+            assert float((h_out.cpu().double() - want_h).abs().max()) < 1e-5
+            assert float((out.float().cpu().double() - want).abs().max()) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
 # ------------------------------------------------------------------------------------------ the attention's edges
 def _edge_case(dtype, hd, hdv, n_q, n_kv, window, keep, n, q_len, probe, sink):
     """A sequence of n keys of which the last q_len are this step's queries; the LAST query points straight at key
@@ -417,6 +442,32 @@ def test_greedy_generation_through_the_library(dtype, gap, graph):
             seq.append(tok)
     engine.cache.check()
     assert engine.cache.free_slots() == 3 and engine.cache.free_pages() == engine.cache.n_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_captured_lone_prompt_equals_the_eager_one(dtype):
+    """A lone prompt whose length comes again is replayed as one captured step (any slot, any start position);
+    its logits must be those of the eager step: bit for bit in float32."""
+    tag = "c"
+    eager = engine_for(tag, dtype)
+    captured = engine_for(tag, dtype, max_batch=4, max_tokens=64 * 24, cuda_graph=True)
+    prompts = [helpers.random_tokens(CFGS[tag]["vocab"], 150, seed=90 + i) for i in range(4)]
+    taken = captured.open()                                   # the replays use another slot than the first run
+    for i, p in enumerate(prompts):
+        want_slot, got_slot = eager.open(), captured.open()
+        want = eager.step([want_slot], [p[:100]], "last")
+        got = captured.step([got_slot], [p[:100]], "last")
+        want2 = eager.step([want_slot], [p[100:]], "last")     # 50 more tokens at start position 100
+        got2 = captured.step([got_slot], [p[100:]], "last")
+        for w_, g_ in ((want, got), (want2, got2)):
+            if dtype == "float32":
+                assert torch.equal(w_, g_), i
+            else:
+                assert float((w_ - g_).abs().max()) <= bound(dtype, w_)
+        eager.close(want_slot)
+        captured.close(got_slot)
+    captured.close(taken)
+    assert any(g and g.graph is not None for g in captured._prefill_graphs.values())
 
 
 def test_long_decoding_in_float32():
