@@ -281,18 +281,35 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
   const T* qs = proj + (size_t)t * ld;
   const T* ks = qs + nq;
   const T* vs = ks + nk;
-  // The first run of 8 query elements of a thread stays in registers between the sum and the store (with one
-  // thread per run, the usual case, q is read once); both sums of squares go through one block reduction.
-  const int i0 = threadIdx.x * 8;
-  float q0[8];
+  // A thread's first runs of 8 elements of q, k and v (with one thread per run, the usual case, all of them) are
+  // requested at once and stay in registers between the sums and the stores: a token's projections are read once, in
+  // one round trip; both sums of squares go through one block reduction.
+  const int i0 = threadIdx.x * 8, step = blockDim.x * 8;
+  // where the token's key and value go: a chain of three dependent loads, started before the data loads so that
+  // it has long returned when the stores need it
+  int page = 0, in_page = 0;
+  if (write_kv) {
+    const int pos = tok_pos[t];
+    page = block_table[(size_t)seq_slot[tok_seq[t]] * max_pages + pos / page_size];
+    in_page = pos % page_size;
+  }
+  float q0[8], k0[8], v0[8], f0[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) q0[e] = 0.f;
+  for (int e = 0; e < 8; ++e) q0[e] = k0[e] = v0[e] = f0[e] = 0.f;
+  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
   if (i0 < nq) load8(qs + i0, q0);
+  if (write_kv) {
+    if (i0 < nk) load8(ks + i0, k0);
+    if (i0 < nv) {
+      load8(vs + i0, v0);
+      if (vf) load8(vf + i0, f0);
+    }
+  }
   float sq = 0.f, sk = 0.f;
   if (q_w) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) sq += q0[e] * q0[e];
-    for (int i = i0 + blockDim.x * 8; i < nq; i += blockDim.x * 8) {
+    for (int i = i0 + step; i < nq; i += step) {
       float x[8];
       load8(qs + i, x);
 #pragma unroll
@@ -300,7 +317,9 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
     }
   }
   if (k_w && write_kv) {
-    for (int i = i0; i < nk; i += blockDim.x * 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sk += k0[e] * k0[e];
+    for (int i = i0 + step; i < nk; i += step) {
       float x[8];
       load8(ks + i, x);
 #pragma unroll
@@ -322,7 +341,7 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
   const float rq = q_w ? 1.f / sqrtf(sq / (float)nq + eps) : 1.f;
   const float rk = (k_w && write_kv) ? 1.f / sqrtf(sk / (float)nk + eps) : 1.f;
   T* qo = q_out + (size_t)t * nq;
-  for (int i = i0; i < nq; i += blockDim.x * 8) {
+  for (int i = i0; i < nq; i += step) {
     float x[8];
     if (i == i0) {
 #pragma unroll
@@ -339,14 +358,15 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
     store8(qo + i, x);
   }
   if (!write_kv) return;
-  const int pos = tok_pos[t];
-  const int slot = seq_slot[tok_seq[t]];
-  const int page = block_table[(size_t)slot * max_pages + pos / page_size];
-  const int in_page = pos % page_size;
-  for (int i = threadIdx.x * 8; i < nk; i += blockDim.x * 8) {
+  for (int i = i0; i < nk; i += step) {
     const int hk = i / hd, e0 = i - hk * hd;
     float x[8];
-    load8(ks + i, x);
+    if (i == i0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = k0[e];
+    } else {
+      load8(ks + i, x);
+    }
     if (k_w) {
       float w8[8];
       load8(k_w + i, w8);
@@ -356,14 +376,20 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
     store8(k_cache + (((size_t)page * n_kv + hk) * page_size + in_page) * hd + e0, x);
   }
   const float lam = v_first ? *lam_ptr : 0.f;
-  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
-  for (int i = threadIdx.x * 8; i < nv; i += blockDim.x * 8) {
+  for (int i = i0; i < nv; i += step) {
     const int hk = i / hdv, e0 = i - hk * hdv;
-    float x[8];
-    load8(vs + i, x);
+    float x[8], f[8];
+    if (i == i0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        x[e] = v0[e];
+        f[e] = f0[e];
+      }
+    } else {
+      load8(vs + i, x);
+      if (vf) load8(vf + i, f);
+    }
     if (vf) {
-      float f[8];
-      load8(vf + i, f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[e] = (1.f - lam) * x[e] + lam * f[e];
     }

@@ -130,10 +130,12 @@ class DeferredBranchAdd:
         return self.h.shape
 
     def foldable(self, weight: torch.Tensor) -> bool:
-        """Whether a product with this bfloat16 weight can do the add itself (one-token steps of up to 8 rows)."""
+        """Whether a product with this bfloat16 weight should do the add itself: one-token steps of as few rows as
+        the fold was measured to pay for (`ops.BRANCH_FOLD_BEST_ROWS`; the kernel takes up to 8)."""
         from ..kernels import ops
         return (getattr(self.norm, "kind", None) == "rmsnorm" and weight.dtype == torch.bfloat16
                 and self.y.dtype == torch.float32 and weight.shape[0] % 16 == 0
+                and self.h.shape[0] <= ops.BRANCH_FOLD_BEST_ROWS
                 and ops.norm_gemm_supported(self.h.shape[0], self.h.shape[1]))
 
     def apply(self, act: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -47,7 +47,7 @@ class BranchNormBlock(Block):
     sits on each branch's OUTPUT. The sum stays float32; a bfloat16 engine's products read the stream rounded to
     bfloat16, and that rounded copy is written by the same kernel that adds the branch (it travels to the next
     layer in `ctx.carry["h_act"]`). A feed-forward that declares `down_bias` has it added inside the norm's
-    kernel. In one-token steps of up to 8 rows of a bfloat16 engine the add is not done here at all: it is handed
+    kernel. In one-token steps of one or two rows of a bfloat16 engine the add is not done here at all: it is handed
     on as a `DeferredBranchAdd` to the part that opens the next branch (the feed-forward, or the next layer's
     mixer, which gets it as `pending`), whose first product does it while it stages its input."""
     ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
@@ -69,7 +69,8 @@ class BranchNormBlock(Block):
 
     def _defers(self, h, ctx) -> bool:
         """Whether the adds of this step are handed on instead of done: one-token steps the fused product takes."""
-        return self.runtime.dtype == torch.bfloat16 and ctx.decode and ops.norm_gemm_supported(h.shape[0], h.shape[1])
+        return (self.runtime.dtype == torch.bfloat16 and ctx.decode and h.shape[0] <= ops.BRANCH_FOLD_BEST_ROWS
+                and ops.norm_gemm_supported(h.shape[0], h.shape[1]))
 
     def _close(self, h, y, bias, norm, ctx, nxt):
         """Ends a branch: h += norm(y + bias), here, or handed to `nxt` (the part that opens the next branch, None =
