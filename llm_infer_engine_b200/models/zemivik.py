@@ -45,7 +45,9 @@ def zemivik_spec(cfg: ZemivikConfig) -> ModelSpec:
         hidden_size=cfg.width, vocab_size=cfg.vocab, max_position=cfg.max_positions, layers=layers,
         schedule=[LayerCall(i) for i in range(len(layers))], final_norm=norm, tie_head=False, embedding_name="embed",
         layer_prefix="l{i}.", final_norm_name="final.norm", head_name="head", after_embedding=stage,
-        after_embedding_name="")
+        after_embedding_name="",
+        # a checkpoint may hold the blend scalar of a layer that does not blend; nothing reads it
+        ignore_unexpected=(r"l\d+\.mix\.vmix$",))
 
 
 register_architecture("Zemivik", ZemivikConfig, zemivik_spec)

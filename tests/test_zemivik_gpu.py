@@ -247,9 +247,9 @@ def _edge_case(dtype, hd, hdv, n_q, n_kv, window, keep, n, q_len, probe, sink):
 
 
 EDGES = [  # window, kept first, keys, probe, may the last query (position keys - 1) see it
-    (72, 6, 300, 228, True), (72, 6, 300, 227, False),          # just inside and just outside the window
-    (72, 6, 300, 5, True), (72, 6, 300, 6, False),              # the last kept token and the first that is not
-    (72, 6, 300, 0, True), (64, 0, 300, 0, False),              # the very first token, kept or not
+    (80, 5, 300, 220, True), (80, 5, 300, 219, False),          # just inside and just outside the window
+    (80, 5, 300, 4, True), (80, 5, 300, 5, False),              # the last kept token and the first that is not
+    (80, 5, 300, 0, True), (64, 0, 300, 0, False),              # the very first token, kept or not
     (64, 0, 257, 193, True), (64, 0, 257, 192, False),          # the window's edge on a page's edge
     (65, 64, 257, 63, True), (65, 64, 257, 64, False),          # a whole page kept
     (100, 70, 640, 69, True), (100, 70, 640, 70, False),        # kept tokens on the second page, far from the query

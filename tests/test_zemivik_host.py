@@ -127,3 +127,30 @@ def test_plain_mechanisms():
     x = torch.tensor([[3.0, 4.0]])
     assert torch.allclose(plain.rms_norm(x, torch.tensor([1.0, 2.0]), 0.0), torch.tensor([[3.0, 8.0]]) / math.sqrt(12.5))
     assert torch.allclose(plain.blend_values(torch.tensor(2.0), torch.tensor(10.0), torch.tensor(0.25)), torch.tensor(4.0))
+
+
+def test_checkpoint_tensors_that_nothing_reads(tmp_path):
+    """The blend scalar of a layer that does not blend may be in the file or not; any other stray tensor, a missing
+    one or a wrong shape is one error that lists them."""
+    from safetensors.torch import load_file, save_file
+    from llm_infer_engine_b200 import WeightsError, write_random_model
+    from llm_infer_engine_b200.weights.loader import build_model
+    folder = str(tmp_path / "m")
+    write_random_model(plain.TINY_B, folder, seed=5, std=0.05)
+    path = folder + "/model.safetensors"
+    t = load_file(path)
+    assert "l1.mix.vmix" in t and "l0.mix.vmix" not in t          # the random mode writes the first blending layer's
+    model, _ = build_model(folder, torch.float32, "cpu")
+    assert model.blocks[2].mixer.lam is not None and model.blocks[1].mixer.lam is None
+    del t["l1.mix.vmix"]                                             # unused: may be absent
+    t["l0.mix.vmix"] = torch.tensor(0.5, dtype=torch.bfloat16)       # and a layer that does not blend may hold one
+    save_file(t, path)
+    build_model(folder, torch.float32, "cpu")
+    del t["l2.mix.vmix"]                                             # this one is read
+    t["l0.mix.extra"] = torch.zeros(3)
+    t["l0.mix.q.norm"] = torch.ones(5)
+    save_file(t, path)
+    with pytest.raises(WeightsError) as e:
+        build_model(folder, torch.float32, "cpu")
+    assert e.value.missing == ["l2.mix.vmix"] and e.value.unexpected == ["l0.mix.extra"]
+    assert [w[0] for w in e.value.wrong_shape] == ["l0.mix.q.norm"]
