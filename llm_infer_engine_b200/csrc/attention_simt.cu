@@ -172,13 +172,3 @@ extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, cons
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
-
-// The form without options: one head size, no kept first keys, no sink, no gate.
-extern "C" int llmie_attention_paged(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                     const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                                     const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
-                                     int n_kv, int hd, float scale, int window, int dtype, cudaStream_t stream) {
-  if (hd % 16) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  return llmie_attention_paged_ex(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
-                                  page_size, n_tokens, n_q, n_kv, hd, hd, scale, window, 0, 0, nullptr, 0, dtype, stream);
-}

@@ -262,9 +262,12 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ proj, int ld, T* __re
 }
 
 // The same with 16-byte loads and stores, for head sizes and a row pitch that are multiples of 8 (and 16-byte
-// aligned tensors): a thread owns runs of 8 elements; a token's q, k and v are read once for the sums of squares
-// and once more (from L1) for the stores.
-template <typename T>
+// aligned tensors). A token is one block's work and a short chain (loads, one block reduction, stores), so what
+// counts is how many tokens an SM has in flight: blocks are small (128 threads where that covers the query
+// projection with R <= 4 runs of 8 elements a thread) and a thread's runs of q stay in registers between the sum
+// and the store. Keys are read again for the store (from L1), values once. The lookups of the token's cache page,
+// a chain of three dependent loads, are placed so that no data load waits behind them.
+template <typename T, int R>
 __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out,
                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
                                          const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
@@ -281,51 +284,39 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
   const T* qs = proj + (size_t)t * ld;
   const T* ks = qs + nq;
   const T* vs = ks + nk;
-  // A thread's first runs of 8 elements of q, k and v (with one thread per run, the usual case, all of them) are
-  // requested at once and stay in registers between the sums and the stores: a token's projections are read once, in
-  // one round trip; both sums of squares go through one block reduction.
   const int i0 = threadIdx.x * 8, step = blockDim.x * 8;
-  // where the token's key and value go: a chain of three dependent loads, started before the data loads so that
-  // it has long returned when the stores need it
-  int page = 0, in_page = 0;
-  if (write_kv) {
-    const int pos = tok_pos[t];
-    page = block_table[(size_t)seq_slot[tok_seq[t]] * max_pages + pos / page_size];
-    in_page = pos % page_size;
-  }
-  float q0[8], k0[8], v0[8], f0[8];
+  const int pos = write_kv ? tok_pos[t] : 0;
+  const int sq_idx = write_kv ? tok_seq[t] : 0;
+  float q[R][8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) q0[e] = k0[e] = v0[e] = f0[e] = 0.f;
-  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
-  if (i0 < nq) load8(qs + i0, q0);
-  if (write_kv) {
-    if (i0 < nk) load8(ks + i0, k0);
-    if (i0 < nv) {
-      load8(vs + i0, v0);
-      if (vf) load8(vf + i0, f0);
+  for (int r = 0; r < R; ++r) {
+    const int i = i0 + r * step;
+    if (i < nq) {
+      load8(qs + i, q[r]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[r][e] = 0.f;
     }
   }
+  // the second link of the page lookup waits for the first here, with every load of q already on its way
+  const int slot = write_kv ? seq_slot[sq_idx] : 0;
   float sq = 0.f, sk = 0.f;
-  if (q_w) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) sq += q0[e] * q0[e];
-    for (int i = i0 + step; i < nq; i += step) {
-      float x[8];
-      load8(qs + i, x);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
-    }
-  }
   if (k_w && write_kv) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) sk += k0[e] * k0[e];
-    for (int i = i0 + step; i < nk; i += step) {
+    for (int i = i0; i < nk; i += step) {
       float x[8];
       load8(ks + i, x);
 #pragma unroll
       for (int e = 0; e < 8; ++e) sk += x[e] * x[e];
     }
   }
+  if (q_w) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += q[r][e] * q[r][e];
+  }
+  // the third link is requested before the block reduction and has arrived when the stores need it
+  const int page = write_kv ? block_table[(size_t)slot * max_pages + pos / page_size] : 0;
   {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
     sq = warp_sum(sq);
@@ -341,32 +332,25 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
   const float rq = q_w ? 1.f / sqrtf(sq / (float)nq + eps) : 1.f;
   const float rk = (k_w && write_kv) ? 1.f / sqrtf(sk / (float)nk + eps) : 1.f;
   T* qo = q_out + (size_t)t * nq;
-  for (int i = i0; i < nq; i += step) {
-    float x[8];
-    if (i == i0) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = q0[e];
-    } else {
-      load8(qs + i, x);
-    }
-    if (q_w) {
-      float w8[8];
-      load8(q_w + i, w8);
+  for (int r = 0; r < R; ++r) {
+    const int i = i0 + r * step;
+    if (i < nq) {
+      if (q_w) {
+        float w8[8];
+        load8(q_w + i, w8);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = x[e] * rq * w8[e];
+        for (int e = 0; e < 8; ++e) q[r][e] = q[r][e] * rq * w8[e];
+      }
+      store8(qo + i, q[r]);
     }
-    store8(qo + i, x);
   }
   if (!write_kv) return;
+  const int in_page = pos % page_size;
   for (int i = i0; i < nk; i += step) {
     const int hk = i / hd, e0 = i - hk * hd;
     float x[8];
-    if (i == i0) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = k0[e];
-    } else {
-      load8(ks + i, x);
-    }
+    load8(ks + i, x);
     if (k_w) {
       float w8[8];
       load8(k_w + i, w8);
@@ -376,20 +360,14 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
     store8(k_cache + (((size_t)page * n_kv + hk) * page_size + in_page) * hd + e0, x);
   }
   const float lam = v_first ? *lam_ptr : 0.f;
+  const T* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
   for (int i = i0; i < nv; i += step) {
     const int hk = i / hdv, e0 = i - hk * hdv;
-    float x[8], f[8];
-    if (i == i0) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        x[e] = v0[e];
-        f[e] = f0[e];
-      }
-    } else {
-      load8(vs + i, x);
-      if (vf) load8(vf + i, f);
-    }
+    float x[8];
+    load8(vs + i, x);
     if (vf) {
+      float f[8];
+      load8(vf + i, f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[e] = (1.f - lam) * x[e] + lam * f[e];
     }
@@ -532,18 +510,29 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
                    aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache) && aligned16(v_first) &&
                    aligned16(q_w) && aligned16(k_w);
   if (vec) {
-    const dim3 vblock(row_threads((n_q * hd + 7) / 8));
-    if (dtype == LLMIE_F32)
-      launch_k(qk_norm_store_vec_kernel<float>, grid, vblock, 0, stream, (const float*)proj, ld, (float*)q_out,
-               (float*)k_cache, (float*)v_cache, q_w, k_w, eps, lam_ptr, (const float*)v_first, v_first_ld, tok_pos,
-               tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, write_kv);
-    else if (dtype == LLMIE_BF16)
-      launch_k(qk_norm_store_vec_kernel<__nv_bfloat16>, grid, vblock, 0, stream, (const __nv_bfloat16*)proj, ld,
-               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_w, k_w, eps, lam_ptr,
-               (const __nv_bfloat16*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, max_pages,
-               page_size, n_q, n_kv, hd, hdv, write_kv);
-    else
+      // runs of 8 query elements a thread: 128 threads where four runs a thread cover the projection, more threads beyond
+    const int runs = (n_q * hd + 7) / 8;
+    int threads = runs <= 128 ? ((runs + 31) / 32) * 32 : 128;
+    if (runs > 4 * threads) threads = (((runs + 3) / 4 + 31) / 32) * 32;
+    // few tokens (one-token steps): nothing to keep in flight but the token itself, so one run a thread
+    if (n_tokens <= 148 && runs > threads) threads = runs <= 512 ? ((runs + 31) / 32) * 32 : 512;
+    if (threads > 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+    const int per_thread = (runs + threads - 1) / threads;
+    const dim3 vblock(threads);
+#define LLMIE_QKV(T, R)                                                                                              \
+  launch_k(qk_norm_store_vec_kernel<T, R>, grid, vblock, 0, stream, (const T*)proj, ld, (T*)q_out, (T*)k_cache,       \
+           (T*)v_cache, q_w, k_w, eps, lam_ptr, (const T*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, \
+           max_pages, page_size, n_q, n_kv, hd, hdv, write_kv)
+    if (dtype == LLMIE_F32) {
+      if (per_thread <= 1) LLMIE_QKV(float, 1); else if (per_thread == 2) LLMIE_QKV(float, 2); else LLMIE_QKV(float, 4);
+    } else if (dtype == LLMIE_BF16) {
+      if (per_thread <= 1) LLMIE_QKV(__nv_bfloat16, 1);
+      else if (per_thread == 2) LLMIE_QKV(__nv_bfloat16, 2);
+      else LLMIE_QKV(__nv_bfloat16, 4);
+    } else {
       return LLMIE_ERR_DTYPE;
+    }
+#undef LLMIE_QKV
     LLMIE_LAUNCH_CHECK();
     return LLMIE_OK;
   }
