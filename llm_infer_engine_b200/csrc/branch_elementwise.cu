@@ -506,7 +506,8 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
   if (n_tokens == 0) return LLMIE_OK;
   const dim3 grid(n_tokens), block(row_threads(n_q * hd));
   // 16-byte accesses: every run of 8 elements (32 bytes of float32, two accesses of 16) starts on 16 bytes
-  const bool vec = hd % 8 == 0 && hdv % 8 == 0 && ld % 8 == 0 && (!v_first || v_first_ld % 8 == 0) && aligned16(proj) &&
+  const bool vec = hd % 8 == 0 && hdv % 8 == 0 && ld % 8 == 0 && (!v_first || v_first_ld % 8 == 0) &&
+                   n_q * hd <= 8 * 4 * 1024 && aligned16(proj) &&
                    aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache) && aligned16(v_first) &&
                    aligned16(q_w) && aligned16(k_w);
   if (vec) {
@@ -516,7 +517,6 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
     if (runs > 4 * threads) threads = (((runs + 3) / 4 + 31) / 32) * 32;
     // few tokens (one-token steps): nothing to keep in flight but the token itself, so one run a thread
     if (n_tokens <= 148 && runs > threads) threads = runs <= 512 ? ((runs + 31) / 32) * 32 : 512;
-    if (threads > 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
     const int per_thread = (runs + threads - 1) / threads;
     const dim3 vblock(threads);
 #define LLMIE_QKV(T, R)                                                                                              \
