@@ -45,14 +45,25 @@ class KVRequest:
     name: str = "kv"
     v_head_dim: Optional[int] = None
     keep_first: int = 0
+    # n > 0: the values ARE the first n columns of the key rows (a latent that serves as key and value at once);
+    # no value storage is made, `v` is a view into `k`, and v_head_dim is n
+    values_in_keys: int = 0
 
     @property
     def value_dim(self) -> int:
+        if self.values_in_keys:
+            return self.values_in_keys
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
-    def geometry(self) -> Tuple[int, int, int, int, int]:
+    @property
+    def stored_per_position(self) -> int:
+        """Elements one position of one sequence occupies."""
+        return self.n_kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_dim))
+
+    def geometry(self) -> Tuple[int, int, int, int, int, int]:
         """What decides which group's storage serves the request."""
-        return (self.n_kv_heads, self.head_dim, self.window, self.value_dim, self.keep_first if self.window else 0)
+        return (self.n_kv_heads, self.head_dim, self.window, self.value_dim, self.keep_first if self.window else 0,
+                self.values_in_keys)
 
 
 @dataclass(frozen=True)
@@ -100,11 +111,16 @@ class _KVGroup:
         self.table = PageTableHost(n_pages, PAGE_SIZE, max_pages_per_seq, req.window, req.keep_first)
         shape = (len(units), n_pages + 1, req.n_kv_heads, PAGE_SIZE)
         self.k = torch.zeros(shape + (req.head_dim,), dtype=dtype, device=device)
-        self.v = torch.zeros(shape + (req.value_dim,), dtype=dtype, device=device)
+        if req.values_in_keys:
+            if not 0 < req.values_in_keys <= req.head_dim:
+                raise ValueError(f"values_in_keys ({req.values_in_keys}) must be at most head_dim ({req.head_dim})")
+            self.v = self.k[..., :req.values_in_keys]
+        else:
+            self.v = torch.zeros(shape + (req.value_dim,), dtype=dtype, device=device)
         self.block_table = torch.full((n_slots + 1, max_pages_per_seq), n_pages, dtype=torch.int32, device=device)
 
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (0 if self.req.values_in_keys else self.v.numel())) * self.k.element_size()
 
 
 class Cache:

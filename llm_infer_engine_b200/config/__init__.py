@@ -3,7 +3,8 @@ from .registry import (Architecture, ConfigError, architecture_of, known_archite
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .llama import LlamaConfig, RopeScaling
 from .zemivik import ZemivikConfig
+from .dofipel import DofipelConfig
 
 __all__ = ["Architecture", "ConfigError", "architecture_of", "known_architectures", "load_config",
            "read_config_json", "register_architecture", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
-           "LlamaConfig", "RopeScaling", "ZemivikConfig"]
+           "LlamaConfig", "RopeScaling", "ZemivikConfig", "DofipelConfig"]

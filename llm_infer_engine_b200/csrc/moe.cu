@@ -1,0 +1,180 @@
+// The bookkeeping of a routed feed-forward (a mixture of experts); the experts' products themselves are the routed
+// form of grouped_gemm.cu.
+//
+//   route     z = W_r x + b in float32 (a warp per token, each lane a fixed share of the columns, so a token's logits do
+//             not depend on the batch); the `top` largest logits are chosen (ties: the lower index), their weights are
+//             the softmax over the chosen logits alone
+//   sort      the (token, choice) pairs grouped by expert into tiles of `tile` positions, padded per expert; one block,
+//             no host involvement, so the step can be captured: sizes are upper bounds, unused tiles say -1
+//   combine   out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]) in float32, in the order of k
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+constexpr int kRouteWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                 int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int d, int n_experts, int top) {
+  extern __shared__ float z_all[];                 // [kRouteWarps][n_experts]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= n_tokens) return;
+  float* z = z_all + warp * n_experts;
+  const T* xr = x + (size_t)t * d;
+  for (int e = 0; e < n_experts; ++e) {
+    const float* wr = w + (size_t)e * d;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) s = fmaf(to_f32(xr[i]), wr[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float first = 0.f, denom = 0.f, mine = 0.f;      // lane k keeps the k-th chosen logit
+  int mine_id = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+    }
+    if (k == 0) first = best;
+    const float p = expf(best - first);
+    denom += p;
+    if ((k & 31) == lane) { mine = p; mine_id = best_e; }
+    if (lane == 0 && best_e < n_experts) z[best_e] = -INFINITY;
+    __syncwarp();
+    if ((k & 31) == 31 || k == top - 1) {
+      // flush this run of up to 32 choices; the weights are normalised below, once the sum is complete
+      const int base = k & ~31;
+      if (base + lane <= k) {
+        ids[(size_t)t * top + base + lane] = mine_id < n_experts ? mine_id : 0;
+        weights[(size_t)t * top + base + lane] = mine;
+      }
+    }
+  }
+  __syncwarp();
+  const float inv = 1.f / denom;
+  for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int top, int n_experts, int tile, int max_tiles,
+                int* __restrict__ sorted_token, int* __restrict__ sorted_pair, int* __restrict__ tile_group) {
+  extern __shared__ int sm[];                      // counts | offsets | cursor, n_experts each
+  int* counts = sm;
+  int* offsets = sm + n_experts;
+  int* cursor = sm + 2 * n_experts;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int e = tid; e < n_experts; e += nt) counts[e] = cursor[e] = 0;
+  const int cap = max_tiles * tile;
+  for (int i = tid; i < cap; i += nt) { sorted_token[i] = -1; sorted_pair[i] = -1; }
+  for (int i = tid; i < max_tiles; i += nt) tile_group[i] = -1;
+  __syncthreads();
+  for (int i = tid; i < n_pairs; i += nt) {
+    const int e = ids[i];
+    if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e] = off;
+      off += (counts[e] + tile - 1) / tile * tile;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < n_experts; e += nt) {
+    const int t0 = offsets[e] / tile, n = (counts[e] + tile - 1) / tile;
+    for (int j = 0; j < n && t0 + j < max_tiles; ++j) tile_group[t0 + j] = e;
+  }
+  for (int i = tid; i < n_pairs; i += nt) {
+    const int e = ids[i];
+    if (e < 0 || e >= n_experts) continue;
+    const int pos = offsets[e] + atomicAdd(&cursor[e], 1);
+    if (pos < cap) { sorted_pair[pos] = i; sorted_token[pos] = i / top; }
+  }
+}
+
+template <typename TS>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
+                                   const TS* __restrict__ shared_out, float* __restrict__ out, int d, int top,
+                                   size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / d;
+    const int c = (int)(i - t * d);
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) s = fmaf(weights[t * top + k], y[(t * top + k) * d + c], s);
+    if (shared_out) s += to_f32(shared_out[i]);
+    out[i] = s;
+  }
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+// x [T, d] of x_dtype; w float32 [E, d]; bias float32 [E] or null; ids int32 [T, top]; weights float32 [T, top].
+extern "C" int llmie_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int* ids, float* weights,
+                               int n_tokens, int d, int n_experts, int top, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return LLMIE_ERR_BAD_ARG;
+  if (x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
+  const size_t smem = (size_t)kRouteWarps * n_experts * sizeof(float);
+  if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_tokens == 0) return LLMIE_OK;
+  const int blocks = (n_tokens + kRouteWarps - 1) / kRouteWarps;
+  if (x_dtype == LLMIE_F32)
+    launch_k(moe_route_kernel<float>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const float*)x, w, bias, ids, weights, n_tokens, d, n_experts, top);
+  else
+    launch_k(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const __nv_bfloat16*)x, w, bias, ids, weights, n_tokens, d, n_experts, top);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// ids int32 [n_pairs] (pair = token * top + choice); sorted_token, sorted_pair int32 [max_tiles * tile];
+// tile_group int32 [max_tiles]. max_tiles must be at least n_pairs / tile + min(n_pairs, n_experts).
+extern "C" int llmie_moe_sort(const int* ids, int n_pairs, int top, int n_experts, int tile, int max_tiles,
+                              int* sorted_token, int* sorted_pair, int* tile_group, cudaStream_t stream) {
+  if (n_pairs < 0 || top <= 0 || n_experts <= 0 || tile <= 0 || max_tiles <= 0) return LLMIE_ERR_BAD_ARG;
+  const int need = n_pairs / tile + (n_pairs < n_experts ? n_pairs : n_experts);
+  if (max_tiles < need) return LLMIE_ERR_BAD_ARG;
+  const size_t smem = (size_t)3 * n_experts * sizeof(int);
+  if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  launch_k(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, top, n_experts, tile, max_tiles, sorted_token, sorted_pair, tile_group);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// y float32 [T * top, d]; weights float32 [T, top]; shared_out [T, d] of shared_dtype or null; out float32 [T, d].
+extern "C" int llmie_moe_combine(const float* y, const float* weights, const void* shared_out, int shared_dtype,
+                                 float* out, int n_tokens, int d, int top, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || top <= 0) return LLMIE_ERR_BAD_ARG;
+  if (shared_out && shared_dtype != LLMIE_F32 && shared_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * d;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (shared_out && shared_dtype == LLMIE_BF16)
+    launch_k(moe_combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, weights, (const __nv_bfloat16*)shared_out, out, d, top, total);
+  else
+    launch_k(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, weights, (const float*)shared_out, out, d, top, total);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

@@ -303,7 +303,7 @@ class Engine:
         for reqs in self.model.unit_requests:
             for r in reqs:
                 if hasattr(r, "n_kv_heads"):
-                    total += r.n_kv_heads * (r.head_dim + r.value_dim) * esize
+                    total += r.stored_per_position * esize
         return total
 
 

@@ -57,8 +57,10 @@ class KernelPlan:
         every option (scale, window, kept first keys, sink, gate); the CUDA-core split-KV kernel knows scale and
         window. A value head size that differs from the key head size is the plain kernel's alone."""
         scale, window = options.scale, options.window
-        if kv.v.shape[-1] != head_dim:
+        if kv.v.shape[-1] != head_dim or not kv.v.is_contiguous():
             return False
+        if options.scored:
+            return False       # a cap, a bias by distance or a learned sink: kernels that know them are chosen above
         if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16):
             # the tensor-core kernels load the gate 16 bytes at a time: rows that do not start on 16 bytes are
             # applied by a kernel of their own afterwards

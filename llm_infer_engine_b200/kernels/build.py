@@ -30,6 +30,10 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
 FAMILIES: Dict[str, tuple] = {
     "elementwise": ("elementwise.cu", [], []),
     "branch_elementwise": ("branch_elementwise.cu", [], []),
+    "parallel_elementwise": ("parallel_elementwise.cu", [], []),
+    "grouped_gemm": ("grouped_gemm.cu", [], []),
+    "moe": ("moe.cu", [], []),
+    "latent": ("latent.cu", [], []),
     "attention_simt": ("attention_simt.cu", [], []),
     "attention_decode": ("attention_decode.cu", [], []),
     "attention_decode_mma": ("attention_decode_mma.cu", [], []),

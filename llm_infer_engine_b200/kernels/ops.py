@@ -253,33 +253,56 @@ def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, 
 
 def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
                     n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0, keep_first: int = 0,
-                    sink: bool = False, gate: Optional[torch.Tensor] = None):
+                    sink: bool = False, gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                    dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None):
     """Plain attention over the paged cache, one warp per (token, query head).
     q [T, n_q hd]; out [T, n_q hdv]; k_cache [n_pages, n_kv, page_size, hd]; v_cache the same with hdv (the value
     head size, read from its shape). window 0 = all earlier keys; the first `keep_first` keys of a sequence stay
     visible behind the window; `sink` adds a key of score 0 without a value to the softmax; `gate` (rows of
-    n_q hdv elements, possibly a column slice of a wider tensor) multiplies the output by its sigmoid."""
+    n_q hdv elements, possibly a column slice of a wider tensor) multiplies the output by its sigmoid. `softcap` c > 0
+    turns a scaled score s into c tanh(s / c); `dist_bias` (float32 [n_q, L]) adds a number per head and distance
+    (query position - key position; distances >= L - 1 share the last column), after the cap and unscaled;
+    `sink_values` (float32 [n_q]) are the sink's score per head instead of 0. v_cache may be a view of the first hdv
+    columns of k_cache's rows (a latent that is key and value at once)."""
     T = q.shape[0]
     hdv = v_cache.shape[-1]
     _need(q, "q", None, (T, n_q * head_dim))
     _need(out, "out", q.dtype, (T, n_q * hdv))
     _need(k_cache, "k_cache", q.dtype, (None, n_kv, page_size, head_dim))
-    _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], n_kv, page_size, hdv))
+    if v_cache.is_contiguous():
+        _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], n_kv, page_size, hdv))
+        v_ld = hdv
+    else:
+        # rows of hdv elements inside wider rows: every row must start v_ld elements after the one before
+        v_ld = v_cache.stride(-2)
+        if (v_cache.dtype is not q.dtype or tuple(v_cache.shape) != (k_cache.shape[0], n_kv, page_size, hdv)
+                or v_cache.stride(-1) != 1 or v_ld < hdv
+                or v_cache.stride() != (n_kv * page_size * v_ld, page_size * v_ld, v_ld, 1)):
+            raise KernelError("attention_paged: v_cache must be contiguous or a column range of contiguous rows")
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
         _need(t, name, torch.int32)
-    if head_dim > 256 or hdv > 256:
-        raise KernelError(f"attention_paged: head sizes {head_dim} / {hdv} must be at most 256")
+    if head_dim > 1024 or hdv > 1024:
+        raise KernelError(f"attention_paged: head sizes {head_dim} / {hdv} must be at most 1024")
+    bias_len = 0
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32, (n_q, None))
+        bias_len = dist_bias.shape[1]
+    if sink_values is not None:
+        _need(sink_values, "sink_values", torch.float32, (n_q,))
+        sink = True
     gate_ld = 0
     if gate is not None:
         gate_ld = _row_slice(gate, "gate", q.dtype, T, n_q * hdv)
     _work(2 * _nbytes(q) + 1.0 * STEP_HINT["kv_total"] * n_kv * (head_dim + hdv) * q.element_size(),
           2.0 * n_q * (head_dim + hdv) * STEP_HINT["pairs"])
     f = _fn("attention_simt", "llmie_attention_paged_ex",
-            [_c_void_p] * 8 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+            [_c_void_p] * 8 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_float,
+                                              _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tok_pos.data_ptr(),
              tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T,
              n_q, n_kv, head_dim, hdv, float(scale), int(window), int(keep_first), 1 if sink else 0, _ptr(gate),
-             gate_ld, _dt(q, "q"), _stream()), "attention_paged")
+             gate_ld, int(v_ld), float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _dt(q, "q"),
+             _stream()), "attention_paged")
     return out
 
 
@@ -1031,3 +1054,212 @@ def advance_lengths(slots, seq_kvlen, seq_lens, n: int, scratch_slot: int) -> No
     f = _fn("elementwise", "llmie_advance_lengths", [_c_void_p] * 3 + [_c_int, _c_int, _c_void_p])
     _check(f(slots.data_ptr(), seq_kvlen.data_ptr(), seq_lens.data_ptr(), n, scratch_slot, _stream()),
            "advance_lengths")
+
+
+# ------------------------------------------------------------------------------------------ parallel blocks
+def add_dyt(h, d1, d2, alpha, weight, bias, out, rows=None):
+    """h (float32 [T, d]) += d1 + d2 in place when rows is None (either may be None; float32 or bfloat16), then
+    out = tanh(alpha * h) * weight + bias (Dynamic Tanh: a norm that reduces nothing). alpha float32 [1] on the
+    device; weight, bias float32 [d]; out [n_out, d]. With `rows` (int32 [n_out]) only those rows of h + d1 + d2
+    are produced and h is left as it is."""
+    T, d = h.shape
+    n_out = T if rows is None else rows.shape[0]
+    _need(h, "h", torch.float32)
+    _need(alpha, "alpha", torch.float32, (1,))
+    _need(weight, "weight", torch.float32, (d,))
+    _need(bias, "bias", torch.float32, (d,))
+    _need(out, "out", None, (n_out, d))
+    for name, t in (("d1", d1), ("d2", d2)):
+        if t is not None:
+            _need(t, name, None, (T, d))
+    if rows is not None:
+        _need(rows, "rows", torch.int32, (n_out,))
+    _work((2 * _nbytes(h) if rows is None else n_out * d * 4) + _nbytes(d1, d2, out))
+    f = _fn("parallel_elementwise", "llmie_add_dyt",
+            [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+             _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), _ptr(d1), _dt(d1, "d1") if d1 is not None else 0, _ptr(d2),
+             _dt(d2, "d2") if d2 is not None else 0, alpha.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+             out.data_ptr(), _dt(out, "out"), _ptr(rows), n_out, d, _stream()), "add_dyt")
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """out[t, j] = act(gate_up[t, j]) * gate_up[t, ff + j]; gate_up [T, 2 ff], out [T, ff]; act an ACT_* code."""
+    T, ff = out.shape
+    _need(out, "out")
+    _need(gate_up, "gate_up", out.dtype, (T, 2 * ff))
+    _work(_nbytes(gate_up, out))
+    f = _fn("parallel_elementwise", "llmie_gated_act", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(gate_up.data_ptr(), out.data_ptr(), T, ff, int(act), _dt(out, "out"), _stream()), "gated_act")
+    return out
+
+
+def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x (float32) *= scale in place."""
+    _need(x, "x", torch.float32)
+    _work(2 * _nbytes(x))
+    f = _fn("parallel_elementwise", "llmie_scale_rows", [_c_void_p, _c_float, ctypes.c_longlong, _c_void_p])
+    _check(f(x.data_ptr(), float(scale), x.numel(), _stream()), "scale_rows")
+    return x
+
+
+# ------------------------------------------------------------------------------------------ grouped products
+_c_ll = ctypes.c_longlong
+_GROUPED_ARGS = [_c_void_p, _c_ll, _c_ll, _c_void_p, _c_void_p, _c_ll, _c_ll, _c_void_p, _c_ll, _c_ll, _c_void_p,
+                 _c_void_p] + [_c_int] * 10 + [_c_void_p]
+GROUPED_SMALL_ROWS = 64        # up to this many rows the tiles of 16 rows are used
+
+
+def grouped_tile_rows(small: bool) -> int:
+    """Rows per tile of the grouped product's two forms (the sort of a routed call uses the same number)."""
+    return 16 if small else 64
+
+
+def _cols(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-d tensor whose rows are contiguous runs (possibly a column range of a wider tensor)."""
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what}: must be a 2-d CUDA tensor with contiguous rows")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def batched_gemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_group_cols: int, out_group_cols: int,
+                    k: int) -> torch.Tensor:
+    """For every group g < G: out[:, g * out_group_cols : + N] = a[:, g * a_group_cols : + k] @ w[g]^T.
+    a [T, >= (G-1) a_group_cols + k] and out [T, >= (G-1) out_group_cols + N] may be column ranges of wider tensors;
+    w [G, N, k] contiguous, of a's dtype (float32, or bfloat16 with bfloat16 or float32 out). float32 accumulation in
+    the order of k."""
+    G, N, K = w.shape
+    T = a.shape[0]
+    if K != k or a.shape[1] < (G - 1) * a_group_cols + k or out.shape[1] < (G - 1) * out_group_cols + N \
+            or out.shape[0] != T:
+        raise KernelError(f"batched_gemm_nt: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} "
+                          f"do not fit (group columns {a_group_cols} / {out_group_cols})")
+    _need(w, "w", a.dtype)
+    lda, ldc = _cols(a, "a"), _cols(out, "out")
+    _work(_nbytes(w) + T * G * (K * a.element_size() + N * out.element_size()), 2.0 * T * G * N * K)
+    f = _fn("grouped_gemm", "llmie_grouped_gemm_nt", _GROUPED_ARGS)
+    _check(f(a.data_ptr(), lda, a_group_cols, None, w.data_ptr(), N * K, K, out.data_ptr(), ldc, out_group_cols, None,
+             None, 0, G, T, N, K, 0, 0, 1 if T <= GROUPED_SMALL_ROWS else 0, _dt(a, "a"), _dt(out, "out"), _stream()),
+           "batched_gemm_nt")
+    return out
+
+
+def routed_gemm_nt(a, a_rows, w, out, out_rows, tile_group, n_positions: int, small: bool, dual: bool = False,
+                   act: int = ACT_NONE):
+    """The routed form: sorted position p (of n_positions, in tiles of grouped_tile_rows(small)) reads row a_rows[p]
+    of a (p itself when a_rows is None), multiplies by w[tile_group[p // tile]]^T and writes row out_rows[p] of out
+    (p itself when None); -1 anywhere = nothing there. w [E, N or 2 N, K]; dual: w holds [gate | up] rows and the
+    result is act(gate) * up."""
+    E, rows_w, K = w.shape
+    N = rows_w // 2 if dual else rows_w
+    _need(w, "w", a.dtype)
+    _need(tile_group, "tile_group", torch.int32)
+    lda, ldc = _cols(a, "a"), _cols(out, "out")
+    if a.shape[1] != K or out.shape[1] != N:
+        raise KernelError(f"routed_gemm_nt: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    tile = grouped_tile_rows(small)
+    n_tiles = tile_group.shape[0]
+    if n_positions > n_tiles * tile:
+        raise KernelError("routed_gemm_nt: more positions than the tiles hold")
+    for name, t in (("a_rows", a_rows), ("out_rows", out_rows)):
+        if t is not None:
+            _need(t, name, torch.int32)
+            if t.shape[0] < n_positions:
+                raise KernelError(f"routed_gemm_nt: {name} shorter than the positions")
+    _work(_nbytes(w) + n_positions * (K * a.element_size() + N * out.element_size()),
+          2.0 * n_positions * rows_w * K)
+    f = _fn("grouped_gemm", "llmie_grouped_gemm_nt", _GROUPED_ARGS)
+    _check(f(a.data_ptr(), lda, 0, _ptr(a_rows), w.data_ptr(), rows_w * K, K, out.data_ptr(), ldc, 0, _ptr(out_rows),
+             tile_group.data_ptr(), n_tiles, E, n_positions, N, K, 1 if dual else 0, int(act), 1 if small else 0,
+             _dt(a, "a"), _dt(out, "out"), _stream()), "routed_gemm_nt")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ routed feed-forward
+def moe_route(x, w, bias, ids, weights):
+    """Router of a mixture of experts: logits = x @ w^T + bias in float32; ids int32 [T, top] receive the `top`
+    largest (ties: the lower index), weights float32 [T, top] the softmax over those logits alone.
+    x [T, d] float32 or bfloat16; w float32 [E, d]; bias float32 [E] or None."""
+    T, d = x.shape
+    E = w.shape[0]
+    top = ids.shape[1]
+    _need(x, "x")
+    _need(w, "w", torch.float32, (E, d))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (E,))
+    _need(ids, "ids", torch.int32, (T, top))
+    _need(weights, "weights", torch.float32, (T, top))
+    _work(_nbytes(x, w, ids, weights), 2.0 * T * E * d)
+    f = _fn("moe", "llmie_moe_route", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 4 +
+            [_c_void_p])
+    _check(f(x.data_ptr(), _dt(x, "x"), w.data_ptr(), _ptr(bias), ids.data_ptr(), weights.data_ptr(), T, d, E, top,
+             _stream()), "moe_route")
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int, tile: int) -> int:
+    """Tiles that the sorted pairs can need at most: every expert may end with a tile that is partly padding."""
+    return n_pairs // tile + min(n_pairs, n_experts)
+
+
+def moe_sort(ids, n_experts: int, tile: int, sorted_token, sorted_pair, tile_group):
+    """Groups the (token, choice) pairs of ids int32 [T, top] by expert into tiles of `tile` positions: sorted_pair[p]
+    = token * top + choice at position p, sorted_token[p] = token, -1 = padding; tile_group[i] = expert of tile i, -1 =
+    unused. The arrays are sized for moe_max_tiles."""
+    T, top = ids.shape
+    n_tiles = tile_group.shape[0]
+    _need(ids, "ids", torch.int32)
+    _need(tile_group, "tile_group", torch.int32, (n_tiles,))
+    _need(sorted_token, "sorted_token", torch.int32, (n_tiles * tile,))
+    _need(sorted_pair, "sorted_pair", torch.int32, (n_tiles * tile,))
+    f = _fn("moe", "llmie_moe_sort", [_c_void_p] + [_c_int] * 5 + [_c_void_p] * 4)
+    _check(f(ids.data_ptr(), T * top, top, n_experts, tile, n_tiles, sorted_token.data_ptr(), sorted_pair.data_ptr(),
+             tile_group.data_ptr(), _stream()), "moe_sort")
+
+
+def moe_combine(y, weights, shared_out, out):
+    """out[t] = sum_k weights[t, k] * y[t * top + k] (+ shared_out[t]); y float32 [T * top, d]; out float32 [T, d]."""
+    T, top = weights.shape
+    d = out.shape[1]
+    _need(y, "y", torch.float32, (T * top, d))
+    _need(weights, "weights", torch.float32)
+    _need(out, "out", torch.float32, (T, d))
+    if shared_out is not None:
+        _need(shared_out, "shared_out", None, (T, d))
+    _work(_nbytes(y, weights, shared_out, out))
+    f = _fn("moe", "llmie_moe_combine", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
+                                         _c_void_p])
+    _check(f(y.data_ptr(), weights.data_ptr(), _ptr(shared_out),
+             _dt(shared_out, "shared_out") if shared_out is not None else 0, out.data_ptr(), T, d, top, _stream()),
+           "moe_combine")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ latent attention
+def latent_prepare(proj, q_off: int, dkv_off: int, q_out, cache, norm_w, eps: float, table, rot_dims: int, tok_pos,
+                   tok_seq, seq_slot, block_table, page_size: int, n_heads: int, dim: int, rot: int, rank: int,
+                   write: bool):
+    """Per token: the latent's RMS norm, the rotation of the shared key part and of every head's rotated query part,
+    the cache write (rows [latent | rotated key part]) and the rotated query parts into the last `rot` columns of each
+    head of q_out [T, n_heads (rank + rot)]. proj [T, ld] holds the queries from column q_off (heads of dim + rot) and,
+    if `write`, the latent projection from dkv_off (rank + rot). table float32 [P, rot_dims / 2, 2] of (cos, sin)."""
+    T, ld = proj.shape
+    _need(proj, "proj")
+    _need(q_out, "q_out", proj.dtype, (T, n_heads * (rank + rot)))
+    _need(table, "table", torch.float32, (None, rot_dims // 2, 2))
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if q_off + n_heads * (dim + rot) > ld or (write and dkv_off + rank + rot > ld):
+        raise KernelError("latent_prepare: the projections do not fit the rows of proj")
+    if write:
+        _need(cache, "cache", proj.dtype, (None, 1, page_size, rank + rot))
+        _need(norm_w, "norm_w", torch.float32, (rank,))
+    _work(T * (n_heads * 2 * rot + (2 * (rank + rot) if write else 0)) * proj.element_size())
+    f = _fn("latent", "llmie_latent_prepare",
+            [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int] +
+            [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p])
+    _check(f(proj.data_ptr(), ld, q_off, dkv_off if write else 0, q_out.data_ptr(), _ptr(cache) if write else None,
+             _ptr(norm_w) if write else None, float(eps), table.data_ptr(), table.shape[0], rot_dims,
+             tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+             page_size, T, n_heads, dim, rot, rank, 1 if write else 0, _dt(proj, "proj"), _stream()), "latent_prepare")
+    return q_out

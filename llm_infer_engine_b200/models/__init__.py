@@ -1,4 +1,4 @@
-from . import llama, zemivik  # noqa: F401  (register LlamaForCausalLM and Zemivik)
+from . import dofipel, llama, zemivik  # noqa: F401  (register LlamaForCausalLM, Zemivik and Dofipel)
 from .decoder import DecoderModel
 
 __all__ = ["DecoderModel"]

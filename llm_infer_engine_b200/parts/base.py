@@ -40,7 +40,8 @@ class ParamSpec:
     """A checkpoint tensor of a part. `role`: "matrix" (a GEMM operand), "vector" (norm weights,
     biases) or "table" (integers). `init` is how the random-weights mode fills it:
     ("normal",) uses the caller's std, ("ones",), ("zeros",) or ("uniform", lo, hi). The random-weights mode
-    writes optional tensors too."""
+    writes optional tensors too. A negative entry -n of `shape` is a size that the checkpoint decides (any size is
+    accepted, the part reads it from the tensor it is given); the random-weights mode writes n there."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: Tuple = ("normal",)
@@ -57,11 +58,21 @@ class AttentionOptions:
     window: int = 0              # 0 = every earlier key; n = the last n keys, the token's own included
     keep_first: int = 0          # with a window: the first n keys of the sequence stay visible behind it
     sink: bool = False           # one more term exp(0) in the softmax's denominator (a key of score 0, no value)
+    sink_values: Optional[torch.Tensor] = None   # float32 [query heads]: the sink's score per head instead of 0
+    softcap: float = 0.0         # c > 0: a scaled score s becomes c * tanh(s / c)
+    # float32 [query heads, L]: a number per head and distance (query position - key position) added to the score
+    # after the cap, unscaled; distances of L - 1 and more share the last column
+    distance_bias: Optional[torch.Tensor] = None
 
     @property
     def plain(self) -> bool:
         """Only the options every attention kernel knows (scale, window)."""
-        return self.keep_first == 0 and not self.sink
+        return self.keep_first == 0 and not self.sink and not self.scored
+
+    @property
+    def scored(self) -> bool:
+        """Whether an option changes single scores (a cap, a bias by distance, a learned sink)."""
+        return self.softcap > 0 or self.distance_bias is not None or self.sink_values is not None
 
 
 class Part:
@@ -81,10 +92,12 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+    def forward(self, h: torch.Tensor, delta, out: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """h (float32 [T, d]) += delta in place when rows is None; returns norm(h) in the
-        activation dtype. With `rows`, only those rows are produced and h is untouched."""
+        activation dtype. With `rows`, only those rows are produced and h is untouched. `delta` is a tensor, None,
+        or a tuple of two branch outputs that are both added (a block whose branches run side by side); a norm whose
+        kernel adds one tensor calls `single_delta` first."""
         raise NotImplementedError
 
     def add_normed(self, h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -97,6 +110,24 @@ class Norm(Part):
         """A promise of norm(h) for a consumer that can fold the norm into its own first kernel,
         or None when this norm (or this shape) cannot be folded."""
         return None
+
+
+def single_delta(delta):
+    """One tensor for norms whose kernel adds one: the members of a tuple are summed into a float32 member (or a
+    float32 copy of the first) by the residual-add kernel."""
+    if not isinstance(delta, (tuple, list)):
+        return delta
+    parts = [d for d in delta if d is not None]
+    if not parts:
+        return None
+    if len(parts) == 1:
+        return parts[0]
+    from ..kernels import ops
+    parts.sort(key=lambda t: t.dtype != torch.float32)
+    total = parts[0] if parts[0].dtype == torch.float32 else parts[0].to(torch.float32)
+    for d in parts[1:]:
+        ops.residual_add(total, d)
+    return total
 
 
 class DeferredNorm:

@@ -136,3 +136,40 @@ class BranchNormMixerBlock(BranchNormBlock):
 
 register_block("branch_norm", BranchNormBlock)
 register_block("branch_norm_mixer", BranchNormMixerBlock)
+
+
+class ParallelBlock(Block):
+    """u = norm(h); h += mixer(u) + feed_forward(u): ONE norm, both branches read its output, and both are added to
+    the stream together. The two branch outputs travel on as a pair and the next norm's kernel adds them while it
+    reads the stream (the float32 sum h + y1 + y2 is formed there); a branch whose part declares `adds_to_residual`
+    may instead add its output into the stream inside its own last product, which is safe because both branches read
+    the norm's output and not the stream."""
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm": "norm"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        tracing = trace.active()
+        u = self.norm.forward(h, pending)
+        if tracing:
+            trace.push(f"Attn_{ctx.entry}")
+        y1 = call_branch(self.mixer, u, ctx, unit, owns_cache, residual=h)
+        if tracing:
+            trace.pop()
+            trace.push(f"FFN_{ctx.entry}")
+        y2 = call_branch(self.feed_forward, u, ctx, residual=h)
+        if tracing:
+            trace.pop()
+        left = tuple(y for y in (y1, y2) if y is not None)
+        return h, (left if len(left) > 1 else (left[0] if left else None))
+
+
+class ParallelMixerBlock(Block):
+    """The same arrangement for a layer without a feed-forward: h += mixer(norm(h))."""
+    ROLES = {"mixer": "mixer", "norm": "norm"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        u = self.norm.forward(h, pending)
+        return h, call_branch(self.mixer, u, ctx, unit, owns_cache, residual=h)
+
+
+register_block("parallel", ParallelBlock)
+register_block("parallel_mixer", ParallelMixerBlock)

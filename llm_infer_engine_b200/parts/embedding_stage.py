@@ -54,3 +54,19 @@ class EmbeddingStage(Pointwise):
 
 
 register_pointwise("embedding_stage", EmbeddingStage)
+
+
+class Scale(Pointwise):
+    """x *= factor: the logits of designs that scale them (or the embedded tokens). params: factor."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.factor = float(params["factor"])
+
+    def forward(self, x, ctx, rows=None):
+        if self.factor != 1.0:
+            ops.scale_rows(x, self.factor)
+        return x
+
+
+register_pointwise("scale", Scale)

@@ -16,10 +16,21 @@ i // (H / G)), and value heads of size Dv:
 
 Keys are cached normalised and values blended, so a later step reads them as they are. Every constant is a
 parameter; each option has an "off" value, so the part also serves designs that use only some of them.
+
+Three more options change single scores, each off by default:
+
+    s_ij <- c * tanh(s_ij / c)               `softcap` c, after the scale
+    s_ij <- s_ij + B[bucket(i - j), head]    `distance_bias` {rows, far}: a learned table B [rows, heads]; with
+                                             m = rows // 2, bucket(n) = n for n < m, else
+                                             min(rows - 1, m + floor(ln(n / m) / ln(far / m) * (rows - m))): one row
+                                             per distance nearby, rows evenly spaced in log(distance) up to `far`
+                                             beyond, the last row for everything farther; added after the cap, unscaled
+    sink = "learned"                         the sink's score is a learned number per head instead of 0
 """
 from __future__ import annotations
 
-from typing import Dict
+import math
+from typing import Dict, List
 
 import torch
 
@@ -29,7 +40,26 @@ from .base import AttentionOptions, DeferredBranchAdd, Mixer, ParamSpec, registe
 from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm",
-                  "blend": "vmix"}
+                  "blend": "vmix", "distance_bias": "rel", "sink": "sink"}
+
+
+RANDOM_BIAS_ROWS = 16
+
+
+def distance_buckets(rows: int, far: float, longest: int) -> List[int]:
+    """Row of the bias table for each distance 0, 1, 2, ... up to the first distance that reaches the last row (all
+    farther ones share it) or `longest`, whichever comes first. Computed in double precision on the host."""
+    half = rows // 2
+    out = []
+    for n in range(max(1, longest)):
+        if n < half:
+            b = n
+        else:
+            b = min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b == rows - 1:
+            break
+    return out
 
 
 class GatedAttention(Mixer):
@@ -54,8 +84,16 @@ class GatedAttention(Mixer):
         self.window, self.keep_first = int(p.get("window") or 0), int(p.get("keep_first") or 0)
         if not self.window:
             self.keep_first = 0
+        self.learned_sink = p.get("sink") == "learned"
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.distance_bias = p.get("distance_bias")
+        if self.distance_bias is not None:
+            # rows None: the table's height is whatever the checkpoint holds (a random model gets RANDOM_BIAS_ROWS)
+            rows = self.distance_bias.get("rows")
+            self.distance_bias = {"rows": None if rows is None else int(rows), "far": float(self.distance_bias["far"])}
         self.options = AttentionOptions(scale=float(scale) if scale is not None else self.head_dim ** -0.5,
-                                        window=self.window, keep_first=self.keep_first, sink=bool(p.get("sink", False)))
+                                        window=self.window, keep_first=self.keep_first, sink=bool(p.get("sink", False)),
+                                        softcap=self.softcap)
         self.qk_norm_eps = p.get("qk_norm_eps")
         self.gate = bool(p.get("gate", False))
         self.value_blend = p.get("value_blend")
@@ -78,6 +116,12 @@ class GatedAttention(Mixer):
         if self.qk_norm_eps is not None:
             specs[n["q_norm"]] = ParamSpec((self.nq,), role="vector", init=("ones",))
             specs[n["k_norm"]] = ParamSpec((self.nk,), role="vector", init=("ones",))
+        if self.distance_bias is not None:
+            rows = self.distance_bias["rows"]
+            specs[n["distance_bias"]] = ParamSpec((rows if rows is not None else -RANDOM_BIAS_ROWS, self.n_heads),
+                                                  role="vector", init=("uniform", -1.0, 1.0))
+        if self.learned_sink:
+            specs[n["sink"]] = ParamSpec((self.n_heads,), role="vector", init=("uniform", -1.0, 1.0))
         if self.value_blend is not None:
             # only a blending layer reads the scalar; a checkpoint may hold one for the first layer as well
             specs[n["blend"]] = ParamSpec((), role="vector", init=("uniform", 0.2, 0.8),
@@ -95,6 +139,23 @@ class GatedAttention(Mixer):
             self.k_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
         if self.value_blend == "blend":
             self.lam = tensors[n["blend"]].to(torch.float32).reshape(1).contiguous()
+        extra = {}
+        if self.distance_bias is not None:
+            # the table by bucket becomes a table by distance: [heads, L], distances of L - 1 and more share a column
+            table = tensors[n["distance_bias"]].to(torch.float32)
+            rows, far = table.shape[0], self.distance_bias["far"]
+            if rows < 2 or far <= rows // 2:
+                raise ValueError(f"distance bias: a table of {rows} rows needs at least 2 rows and far ({far}) beyond "
+                                 "half of them")
+            longest = self.window if self.window else self.runtime.max_positions
+            buckets = distance_buckets(rows, far, longest)
+            index = torch.tensor(buckets, dtype=torch.long, device=table.device)
+            extra["distance_bias"] = table[index].t().contiguous()
+        if self.learned_sink:
+            extra["sink_values"] = tensors[n["sink"]].to(torch.float32).contiguous()
+        if extra:
+            import dataclasses
+            self.options = dataclasses.replace(self.options, **extra)
 
     def weight_bytes(self) -> int:
         return self.proj.nbytes() + self.o.nbytes() + (4 * (self.nq + self.nk) if self.q_w is not None else 0)

@@ -13,7 +13,9 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
-    """params: hidden, intermediate."""
+    """params: hidden, intermediate; activation (on the gate: "silu", the default, or any of ops.ACTIVATIONS, e.g.
+    "gelu_tanh"); names (checkpoint sub-names of gate, up, down); out_float32 (the branch output is float32 instead
+    of the activations' type: for designs that round nothing between the last product and the residual sum)."""
 
     adds_to_residual = True
     accepts_deferred_norm = True
@@ -22,19 +24,27 @@ class SwiGLU(FeedForward):
         super().__init__(params, runtime)
         self.hidden = int(params["hidden"])
         self.intermediate = int(params["intermediate"])
+        name = str(params.get("activation", "silu"))
+        if name not in ops.ACTIVATIONS or name == "none":
+            raise ValueError(f"activation {name!r} is not known ({sorted(ops.ACTIVATIONS)})")
+        self.activation = ops.ACTIVATIONS[name]
+        self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"},
+                          **(params.get("names") or {}))
+        self.out_float32 = bool(params.get("out_float32", False))
         self.gate_up: Linear = None
         self.down: Linear = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"gate_proj.weight": ParamSpec((self.intermediate, self.hidden)),
-                "up_proj.weight": ParamSpec((self.intermediate, self.hidden)),
-                "down_proj.weight": ParamSpec((self.hidden, self.intermediate))}
+        n = self.names
+        return {n["gate"]: ParamSpec((self.intermediate, self.hidden)),
+                n["up"]: ParamSpec((self.intermediate, self.hidden)),
+                n["down"]: ParamSpec((self.hidden, self.intermediate))}
 
     def load(self, tensors):
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         dtype = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.gate_up = Linear(torch.cat([g.to(dtype), u.to(dtype)], dim=0))
-        self.down = Linear(tensors["down_proj.weight"])
+        self.down = Linear(tensors[self.names["down"]])
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
@@ -50,21 +60,25 @@ class SwiGLU(FeedForward):
         act = None
         if isinstance(x, DeferredNorm):
             w = self.gate_up.weight
-            if x.kind == "rmsnorm" and w.dtype == torch.bfloat16 and self.intermediate % 8 == 0:
+            if x.kind == "rmsnorm" and w.dtype == torch.bfloat16 and self.intermediate % 8 == 0 \
+                    and self.activation == ops.ACT_SILU:
                 # one-token steps: norm, product, activation and gate in one kernel
                 act = torch.empty((x.shape[0], self.intermediate), dtype=torch.bfloat16, device=w.device)
                 ops.norm_gate_swiglu(x.h, x.weight, x.eps, w, act)
             else:
                 x = x.apply()
-        if act is None:
+        if act is None and self.activation == ops.ACT_SILU:
             act = self.gate_up.swiglu(x)             # product, activation and gate in one kernel
         if act is None:
             gu = self.gate_up(x)
             act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
-            ops.swiglu(gu, act)
+            if self.activation == ops.ACT_SILU:
+                ops.swiglu(gu, act)
+            else:
+                ops.gated_act(gu, act, self.activation)
         if residual is not None and self.down.add_into(act, residual):
             return None
-        return self.down(act)
+        return self.down(act, out_dtype=torch.float32) if self.out_float32 else self.down(act)
 
 
 register_feed_forward("swiglu", SwiGLU)

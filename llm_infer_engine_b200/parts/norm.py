@@ -10,7 +10,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops, trace
-from .base import DeferredNorm, Norm, ParamSpec, register_norm
+from .base import DeferredNorm, Norm, ParamSpec, register_norm, single_delta
 
 
 class RMSNorm(Norm):
@@ -46,6 +46,13 @@ class RMSNorm(Norm):
         if out is None:
             out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=h.device)
         trace.push("RMSNorm")
+        delta = single_delta(delta)
+        if delta is not None and delta.dtype != out.dtype:
+            # the fused kernel adds a branch output of the activations' type; any other is added by a kernel of its own
+            if rows is not None:
+                h = h.clone()
+            ops.residual_add(h, delta)
+            delta = None
         ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         trace.pop()
         return out
@@ -59,3 +66,50 @@ class RMSNorm(Norm):
 
 
 register_norm("rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * w + b, element by element: a norm that computes no mean and no variance, so nothing is
+    reduced over a row. alpha is a learned scalar, w and b learned vectors; float32 arithmetic, one rounding at the
+    store. The kernel adds up to two branch outputs to the stream on the way (`delta` may be a tuple).
+
+    params: size; weight_name (default "weight"; "" = the part's own name), alpha_name (default "alpha"), bias_name
+    (default "b"): the tensors' names under the part's checkpoint name."""
+
+    kind = "dynamic_tanh"
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.size = int(params["size"])
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.alpha_name = str(params.get("alpha_name", "alpha"))
+        self.bias_name = str(params.get("bias_name", "b"))
+        self.weight = self.alpha = self.bias = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.size,), role="vector", init=tuple(self.params.get("init", ("ones",)))),
+                self.alpha_name: ParamSpec((), role="vector", init=("uniform", 0.3, 0.9)),
+                self.bias_name: ParamSpec((self.size,), role="vector", init=("uniform", -0.1, 0.1))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name].to(torch.float32).contiguous()
+        self.alpha = tensors[self.alpha_name].to(torch.float32).reshape(1).contiguous()
+        self.bias = tensors[self.bias_name].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.size * 8 + 4
+
+    def forward(self, h, delta, out=None, rows=None):
+        n_out = h.shape[0] if rows is None else rows.shape[0]
+        if out is None:
+            out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=h.device)
+        d = [x for x in (delta if isinstance(delta, (tuple, list)) else (delta,)) if x is not None]
+        if len(d) > 2:
+            raise ValueError("DynamicTanh adds at most two branch outputs")
+        trace.push("DyT")
+        ops.add_dyt(h, d[0] if d else None, d[1] if len(d) > 1 else None, self.alpha, self.weight, self.bias, out, rows)
+        trace.pop()
+        return out
+
+
+register_norm("dynamic_tanh", DynamicTanh)

@@ -61,7 +61,9 @@ def compare(expected: Dict[str, tuple], found: Dict[str, tuple], ignore: List[st
     patterns = [re.compile(p) for p in ignore]
     missing = sorted(n for n in expected if n not in found)
     unexpected = sorted(n for n in found if n not in expected and not any(p.match(n) for p in patterns))
-    wrong = sorted((n, expected[n], found[n]) for n in expected if n in found and tuple(found[n]) != tuple(expected[n]))
+    def fits(want, got):          # a negative entry of an expected shape is a size the checkpoint decides
+        return len(want) == len(got) and all(w < 0 or w == g for w, g in zip(want, got))
+    wrong = sorted((n, expected[n], found[n]) for n in expected if n in found and not fits(tuple(expected[n]), tuple(found[n])))
     if missing or unexpected or wrong:
         raise WeightsError(where, missing, unexpected, wrong)
 

@@ -9,6 +9,7 @@ values do not depend on the others. Values are stored in bfloat16 unless `dtype`
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 from typing import Optional, Tuple
@@ -36,6 +37,8 @@ def random_tensors(config_json: dict, seed: int, std: float = 0.02,
     for index, (name, ps) in enumerate(sorted(model.param_specs().items())):
         g = torch.Generator().manual_seed((int(seed) * 1000003 + index) & 0x7FFFFFFFFFFFFFFF)
         kind = ps.init[0]
+        if any(n < 0 for n in ps.shape):
+            ps = dataclasses.replace(ps, shape=tuple(abs(n) for n in ps.shape))
         if ps.role == "vector" and norm_range is not None and kind == "ones":
             t = torch.empty(ps.shape).uniform_(float(norm_range[0]), float(norm_range[1]), generator=g)
         elif kind == "ones":

@@ -53,7 +53,7 @@ def test_a_unit_holds_several_named_requests():
     unit1 = [KVRequest(2, 16, 0), KVRequest(2, 16, 8, name="local")]          # two requests, two groups
     unit2 = [KVRequest(2, 16, 0, name="a"), KVRequest(2, 16, 0, name="b")]    # two requests of one geometry
     cache = Cache([unit0, unit1, unit2], n_slots=3, max_tokens=64 * 4, max_seq_len=128, dtype=torch.float32, device="cpu")
-    assert sorted(r.geometry() for r in cache.groups()) == [(2, 16, 0, 16, 0), (2, 16, 8, 16, 0)]
+    assert sorted(r.geometry() for r in cache.groups()) == [(2, 16, 0, 16, 0, 0), (2, 16, 8, 16, 0, 0)]
     u0, u1, u2 = cache.unit(0), cache.unit(1), cache.unit(2)
     assert sorted(u0.kvs) == ["attn.kv"] and u0.kv is u0.kvs["attn.kv"]        # the only one there is
     assert u0.scoped("rec").state["s"].shape == (4, 5) and u0.scoped("rec").state["t"].shape == (4, 2, 3)
