@@ -398,6 +398,35 @@ def zemivik_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
                        for _ in range(n_layers)]}
 
 
+def dofipel_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int, n_layers: int,
+                   window: int) -> dict:
+    """A Dofipel configuration with a Llama shape's layer sizes. Layers cycle through its four kinds: windowed
+    attention + gated feed-forward, latent attention + routed experts, latent attention that reads the layer
+    before's latent + gated feed-forward, windowed attention + routed experts. The routed feed-forward's active
+    width (3 of 16 experts of ff / 4, plus a shared expert of ff / 4) equals the dense one's; the latent is
+    4 head sizes wide with a rotated part of half a head size."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "softcap": 30.0, "bias_max": 2048, "mask": {"size": window} if window else None}
+    rot = head_dim // 2
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": rot, "vdim": head_dim, "kv_rank": 4 * head_dim,
+              "scale": (head_dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 3}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    layers = []
+    for i in range(n_layers):
+        kind = i % 4
+        if kind == 0:
+            layers.append({"type": "attention", "mixer": dict(attn), "mlp": dense})
+        elif kind == 1:
+            layers.append({"type": "latent_attention", "mixer": dict(latent), "mlp": moe})
+        elif kind == 2:
+            layers.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 1), "mlp": dense})
+        else:
+            layers.append({"type": "attention", "mixer": dict(attn), "mlp": moe})
+    return {"architecture": "Dofipel", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
 def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
     """Per-kernel tables (eager steps, CUDA events) of a decode step at `batch` sequences and of a 2,048-token
     prompt."""
@@ -435,8 +464,8 @@ def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
     return "\n".join(parts)
 
 
-def run_designs(args, pk: dict) -> str:
-    """Zemivik beside Llama at equal layer sizes (random weights, bfloat16): decode throughput at batch 1, 8 and 64
+def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
+    """Zemivik (or, with which="Dofipel", Dofipel with a window of 1,024) beside Llama at equal layer sizes (random weights, bfloat16): decode throughput at batch 1, 8 and 64
     after 512-token prompts (captured steps, device time), prefill throughput of one 2,048-token prompt, and the
     per-kernel tables of both. Zemivik once without a mask (the attention work of Llama's) and once with a window
     of 1,024 tokens that keeps the first four. The shared vocabulary is kept small so that the layers, not the
@@ -448,7 +477,7 @@ def run_designs(args, pk: dict) -> str:
     vocab = 32000
     shapes = [("1B layer sizes", CONFIG_1B), ("8B layer sizes", CONFIG_8B)]
     steps = min(args.steps, 64)
-    lines = [f"Zemivik beside Llama at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
+    lines = [f"{which} beside Llama at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
              f"(peaks: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s, {pk['source']}).", "",
              "| layer sizes | design | decode b1 tok/s | ms/step | decode b8 tok/s | ms/step | decode b64 tok/s | ms/step | "
              f"prefill {PREFILL_TOKENS} tok/s | ms |", "|---|---|---|---|---|---|---|---|---|---|"]
@@ -461,6 +490,9 @@ def run_designs(args, pk: dict) -> str:
         designs = [("Llama", llama),
                    ("Zemivik, no mask", zemivik_config(d, hq, hkv, hd, ff, vocab, n_layers, 0, 0)),
                    ("Zemivik, window 1024 + 4", zemivik_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024, 4))]
+        if which == "Dofipel":
+            designs = [("Llama", llama),
+                       ("Dofipel, window 1024", dofipel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024))]
         for design, cfg in designs:
             folder = scratch_folder("llmie_bench_design_")
             write_random_model(cfg, folder, seed=3, std=0.02)
@@ -582,8 +614,8 @@ def run_ours(args):
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
                 f.write(text + "\n")
         return 0
-    if args.designs:
-        text = run_designs(args, pk)
+    if args.designs or args.dofipel:
+        text = run_designs(args, pk, "Dofipel" if args.dofipel else "Zemivik")
         print(text)
         if args.per_kernel_out:
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
@@ -755,6 +787,9 @@ def main():
     ap.add_argument("--designs", action="store_true",
                     help="Zemivik beside Llama at equal layer sizes: decode and prefill throughput and per-kernel tables "
                          "(prints markdown; --layers sets the depth, default 4)")
+    ap.add_argument("--dofipel", action="store_true",
+                    help="the same comparison for Dofipel (windowed and latent attention, gated and routed "
+                         "feed-forwards) beside Llama")
     ap.add_argument("--heads", type=int, default=32, help="query heads of --attention-sweep")
     ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of --attention-sweep")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="head size of --attention-sweep")

@@ -60,20 +60,34 @@ __device__ __forceinline__ unsigned md_pack(float a, float b) {
 // Options beyond (scale, window), each off at 0 / null: the first keep_first keys of a sequence stay visible behind
 // the window; sink: one more softmax term of score 0 that has no value; gate: bfloat16 rows of n_q * HD elements,
 // gate_ld apart, whose sigmoid multiplies the output.
+// Three more change single scores: softcap c > 0 turns a scaled score s into c * tanh(s / c); dist_bias (float32
+// [n_q, bias_len]) adds a number per query head and distance (distances of bias_len - 1 and more share the last entry)
+// after the cap; sink_vals (float32 [n_q]) is the sink's score per head instead of 0.
 struct MdOptions {
   int keep_first;
   int sink;
   const __nv_bfloat16* gate;
   int gate_ld;
+  float softcap;
+  const float* dist_bias;
+  int bias_len;
+  const float* sink_vals;
 };
+
+__device__ __forceinline__ float md_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // The last step of a (sequence, head)'s softmax: numerator and denominator relative to the maximum M (log2 units).
 // With a sink the denominator gains 2^(0 - M'), M' = max(M, 0).
-__device__ __forceinline__ float md_finish(float num, float den, float M, int sink) {
+// `sv` is the sink's score in log2 units (0 unless given per head).
+__device__ __forceinline__ float md_finish(float num, float den, float M, int sink, float sv = 0.f) {
   if (sink) {
-    const float Mx = fmaxf(M, 0.f);
+    const float Mx = fmaxf(M, sv);
     const float f = md_exp2(M - Mx);
-    return num * f / (den * f + md_exp2(-Mx));
+    return num * f / (den * f + md_exp2(sv - Mx));
   }
   return num / den;
 }
@@ -87,7 +101,7 @@ __device__ __forceinline__ float md_gated(float v, const __nv_bfloat16* gate_row
 template <int HD>
 __device__ __forceinline__ void md_merge_head(const float* part_m, const float* part_l, const float* part_acc,
                                               __nv_bfloat16* out_row, size_t base, int r0, int r1, int extra, int sink,
-                                              const __nv_bfloat16* gate_row) {
+                                              const __nv_bfloat16* gate_row, float sv = 0.f) {
   const int lane = threadIdx.x & 31;
   const int n = extra + r1 - r0 + 1;
   auto run_of = [&](int i) { return i < extra ? i : r0 + i - extra; };
@@ -118,7 +132,7 @@ __device__ __forceinline__ void md_merge_head(const float* part_m, const float* 
   denom = warp_sum(denom);
 #pragma unroll
   for (int k = 0; k < HD / 32; ++k)
-    out_row[lane + 32 * k] = __float2bfloat16_rn(md_gated(md_finish(num[k], denom, M, sink), gate_row, lane + 32 * k));
+    out_row[lane + 32 * k] = __float2bfloat16_rn(md_gated(md_finish(num[k], denom, M, sink, sv), gate_row, lane + 32 * k));
 }
 
 // grid (n_runs, n_kv * chunks, n_seqs), chunks = ceil(G / 16); WARPS warps per block.
@@ -256,6 +270,11 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   float l_lo = 0.f, l_hi = 0.f;                        // this lane's share of the running sums
 
   const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
+  const bool scored = opt.softcap > 0.f || opt.dist_bias != nullptr;
+  const float inv_cap = opt.softcap > 0.f ? 1.f / opt.softcap : 0.f;
+  // rows g and g + 8 of the query tile are query heads hk * G + g0 + g (+ 8); rows beyond the group read row 0's table
+  const float* bias_lo = opt.dist_bias ? opt.dist_bias + (size_t)(hk * G + g0 + (g < ng ? g : 0)) * opt.bias_len : nullptr;
+  const float* bias_hi = opt.dist_bias ? opt.dist_bias + (size_t)(hk * G + g0 + (g + 8 < ng ? g + 8 : 0)) * opt.bias_len : nullptr;
   // ldmatrix row addresses: lane i gives row (i & 7) of matrix (i >> 3)
   const int lm_r = lane & 7, lm_m = lane >> 3;
   for (int idx = 0; p <= p_last; ++idx) {
@@ -325,8 +344,24 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
       for (int c = 0; c < 2; ++c) {
         const int key = nt * 8 + 2 * t + c;
         const bool vis = (key >= first && key < last) || key < kept_here;
-        s[nt][c] = vis ? s[nt][c] * scale2 : -INFINITY;
-        s[nt][2 + c] = vis ? s[nt][2 + c] * scale2 : -INFINITY;
+        if (scored) {
+          // the cap and the bias by distance work on the scaled score itself; then into log2 units
+          float a = s[nt][c] * scale, b = s[nt][2 + c] * scale;
+          if (opt.softcap > 0.f) {
+            a = opt.softcap * md_tanh(a * inv_cap);
+            b = opt.softcap * md_tanh(b * inv_cap);
+          }
+          if (opt.dist_bias) {
+            const int dist = min(max(len - 1 - (p * kMdPage + h * kHalf + key), 0), opt.bias_len - 1);
+            a += bias_lo[dist];
+            b += bias_hi[dist];
+          }
+          s[nt][c] = vis ? a * 1.4426950408889634f : -INFINITY;
+          s[nt][2 + c] = vis ? b * 1.4426950408889634f : -INFINITY;
+        } else {
+          s[nt][c] = vis ? s[nt][c] * scale2 : -INFINITY;
+          s[nt][2 + c] = vis ? s[nt][2 + c] * scale2 : -INFINITY;
+        }
         mx_lo = fmaxf(mx_lo, s[nt][c]);
         mx_hi = fmaxf(mx_hi, s[nt][2 + c]);
       }
@@ -422,7 +457,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
     if (n_runs == 1) {
       const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
-      out[head * HD + d] = __float2bfloat16_rn(md_gated(md_finish(num, den, M, opt.sink), gate_row, d));
+      const float sv = opt.sink_vals ? opt.sink_vals[(size_t)hk * G + g0 + row] * 1.4426950408889634f : 0.f;
+      out[head * HD + d] = __float2bfloat16_rn(md_gated(md_finish(num, den, M, opt.sink, sv), gate_row, d));
     } else {
       part_acc[(head * n_runs + run) * HD + d] = num;
       if (d == 0) {
@@ -449,7 +485,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   for (int row = warp; row < ng; row += WARPS) {
     const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
     const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
-    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1, extra, opt.sink, gate_row);
+    const float sv = opt.sink_vals ? opt.sink_vals[(size_t)hk * G + g0 + row] * 1.4426950408889634f : 0.f;
+    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1, extra, opt.sink, gate_row, sv);
   }
 }
 
@@ -575,7 +612,7 @@ extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, co
                                           cudaStream_t stream) {
   return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
                           max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
-                          0, 0, MdOptions{0, 0, nullptr, 0}, stream);
+                          0, 0, MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr}, stream);
 }
 
 // The same with the options of MdOptions: kept first keys, a sink, an output gate.
@@ -584,10 +621,14 @@ extern "C" int llmie_attention_decode_mma_ex(const void* q, const void* k_cache,
                                              const int* seq_slot, const int* seq_kvlen, const int* block_table,
                                              int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
                                              float scale, int window, int pages_per_run, int n_runs, int keep_first,
-                                             int sink, const void* gate, int gate_ld, cudaStream_t stream) {
+                                             int sink, const void* gate, int gate_ld, float softcap,
+                                             const float* dist_bias, int bias_len, const float* sink_vals,
+                                             cudaStream_t stream) {
+  if (softcap < 0.f || (dist_bias && bias_len <= 0) || (sink_vals && !sink)) return LLMIE_ERR_BAD_ARG;
   return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
                           max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
-                          0, 0, MdOptions{keep_first, sink ? 1 : 0, (const __nv_bfloat16*)gate, gate_ld}, stream);
+                          0, 0, MdOptions{keep_first, sink ? 1 : 0, (const __nv_bfloat16*)gate, gate_ld, softcap, dist_bias,
+                                          bias_len, sink_vals}, stream);
 }
 
 // The same with position encoding and the cache write inside: qkv bfloat16 [n_seqs, (n_q + 2 n_kv) hd] holds the
@@ -606,5 +647,5 @@ extern "C" int llmie_attention_decode_mma_rope(const void* qkv, void* k_cache, v
   return decode_mma_entry(qkv, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen,
                           block_table, max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs,
                           reinterpret_cast<const float2*>(rope), table_len, (n_q + 2 * n_kv) * hd, write_kv ? 1 : 0,
-                          MdOptions{0, 0, nullptr, 0}, stream);
+                          MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr}, stream);
 }

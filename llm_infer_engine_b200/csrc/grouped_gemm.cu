@@ -9,8 +9,9 @@
 //             C it writes): the experts of a routed feed-forward. Positions without an indirection are their own row.
 //
 // W is [groups][N (or 2 N), K], K contiguous. With DUAL the weight of a group is [gate rows | up rows] and the result
-// is act(A gate^T) * (A up^T). Accumulation is float32 with one FMA per k in the order k = 0..K-1 whatever the tile or
-// the batch, so a row's result does not depend on what else is in the launch; inputs may be float32 or bfloat16.
+// is act(A gate^T) * (A up^T). float32 inputs: one FMA per k in the order k = 0..K-1 whatever the tile or the batch (no
+// tensor cores, no reduced precision), so a row's result does not depend on what else is in the launch. bfloat16 inputs:
+// the tensor-core kernel further down, float32 accumulators.
 #include "common.cuh"
 
 namespace llmie {
@@ -118,6 +119,132 @@ grouped_gemm_kernel(const GroupedArgs p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// The same products for bfloat16 inputs on the tensor cores (mma.sync m16n8k16, float32 accumulators): tiles of
+// BM x 64 outputs, four warps. With BM = 64 a warp owns 16 rows and all 64 columns; with BM = 16 (few rows a group:
+// one-token steps, where the weights are what is streamed) the warps share out the columns and the K step is longer.
+// A row's sums depend on that row and the weights alone (the rows of an mma are independent), so here too a result
+// does not depend on what else is in the launch. `vec`: K, the leading dimensions and the group strides are multiples
+// of 8 elements and the bases 16-byte aligned, so tiles are fetched 16 bytes at a time; otherwise element by element.
+__device__ __forceinline__ void gg_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TC, int BM, int BK, bool DUAL>
+__global__ void __launch_bounds__(128)
+grouped_gemm_mma_kernel(const GroupedArgs p, const int vec) {
+  constexpr int BN = 64, PITCH = BK + 8, NW = DUAL ? 2 : 1, CH = BK / 8;
+  constexpr int NT = BM == 64 ? 8 : 2;                 // n-tiles of 8 columns a warp owns
+  __shared__ __align__(16) __nv_bfloat16 As[BM][PITCH];
+  __shared__ __align__(16) __nv_bfloat16 Ws[NW][BN][PITCH];
+  __shared__ int rowA[BM], rowC[BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int tile = blockIdx.y;
+  int group = blockIdx.z;
+  if (p.tile_group) {
+    group = p.tile_group[tile];
+    if (group < 0) return;
+  }
+  const int m0 = tile * BM, n0 = blockIdx.x * BN;
+  for (int r = tid; r < BM; r += 128) {
+    const int pos = m0 + r;
+    int ra = -1, rc = -1;
+    if (pos < p.M) {
+      ra = p.a_rows ? p.a_rows[pos] : pos;
+      rc = p.c_rows ? p.c_rows[pos] : pos;
+      if (ra < 0 || rc < 0) ra = rc = -1;
+    }
+    rowA[r] = ra;
+    rowC[r] = rc;
+  }
+  __syncthreads();
+  const __nv_bfloat16* A = reinterpret_cast<const __nv_bfloat16*>(p.A) + (size_t)group * p.a_gcs;
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W) + (size_t)group * p.w_gs;
+  const int row0 = BM == 64 ? warp * 16 : 0;
+  const int nt0 = BM == 64 ? 0 : warp * 2;
+  float acc[NW][NT][4];
+#pragma unroll
+  for (int s = 0; s < NW; ++s)
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
+
+  // eight consecutive elements of a row from column gk on (zeros beyond K or for a row that is not there)
+  auto fetch = [&](const __nv_bfloat16* row, bool there, int gk) -> uint4 {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (!there || gk >= p.K) return v;
+    if (vec) return *reinterpret_cast<const uint4*>(row + gk);
+    __nv_bfloat16 e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = gk + i < p.K ? row[gk + i] : __float2bfloat16_rn(0.f);
+    return *reinterpret_cast<const uint4*>(e);
+  };
+
+  for (int k0 = 0; k0 < p.K; k0 += BK) {
+    for (int c = tid; c < BM * CH; c += 128) {
+      const int r = c / CH, kc = (c % CH) * 8;
+      const int ra = rowA[r];
+      *reinterpret_cast<uint4*>(&As[r][kc]) = fetch(A + (size_t)(ra < 0 ? 0 : ra) * p.lda, ra >= 0, k0 + kc);
+    }
+    for (int c = tid; c < BN * CH; c += 128) {
+      const int r = c / CH, kc = (c % CH) * 8;
+      const int gn = n0 + r;
+      *reinterpret_cast<uint4*>(&Ws[0][r][kc]) = fetch(W + (size_t)gn * p.ldw, gn < p.N, k0 + kc);
+      if (DUAL) *reinterpret_cast<uint4*>(&Ws[NW - 1][r][kc]) = fetch(W + (size_t)(gn + p.N) * p.ldw, gn < p.N, k0 + kc);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      const unsigned a0 = *reinterpret_cast<const unsigned*>(&As[row0 + g][kk + 2 * t]);
+      const unsigned a1 = *reinterpret_cast<const unsigned*>(&As[row0 + g + 8][kk + 2 * t]);
+      const unsigned a2 = *reinterpret_cast<const unsigned*>(&As[row0 + g][kk + 2 * t + 8]);
+      const unsigned a3 = *reinterpret_cast<const unsigned*>(&As[row0 + g + 8][kk + 2 * t + 8]);
+#pragma unroll
+      for (int s = 0; s < NW; ++s)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(&Ws[s][(nt0 + i) * 8 + g][kk + 2 * t]);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(&Ws[s][(nt0 + i) * 8 + g][kk + 2 * t + 8]);
+          gg_mma(acc[s][i], a0, a1, a2, a3, b0, b1);
+        }
+    }
+    __syncthreads();
+  }
+  TC* C = reinterpret_cast<TC*>(p.C) + (size_t)group * p.c_gcs;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int rc = rowC[row0 + g + 8 * half];
+    if (rc < 0) continue;
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int gn = n0 + (nt0 + i) * 8 + 2 * t + e;
+        if (gn >= p.N) continue;
+        float v = acc[0][i][2 * half + e];
+        if (DUAL) {
+          const float gt = to_f32(from_f32<TC>(v)), up = to_f32(from_f32<TC>(acc[NW - 1][i][2 * half + e]));
+          v = apply_act(gt, p.act) * up;
+        }
+        C[(size_t)rc * p.ldc + gn] = from_f32<TC>(v);
+      }
+  }
+}
+
+template <typename TC, bool DUAL>
+static int launch_grouped_mma(const GroupedArgs& p, int n_tiles, int groups_z, bool small, int vec, cudaStream_t stream) {
+  dim3 grid((p.N + 63) / 64, n_tiles, groups_z);
+  if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (small) launch_k(grouped_gemm_mma_kernel<TC, 16, 64, DUAL>, grid, dim3(128), 0, stream, p, vec);
+  else launch_k(grouped_gemm_mma_kernel<TC, 64, 32, DUAL>, grid, dim3(128), 0, stream, p, vec);
+  return LLMIE_OK;
+}
+
 template <typename TA, typename TC, bool DUAL>
 static int launch_grouped(const GroupedArgs& p, int n_tiles_small, int n_tiles_big, int groups_z, bool small,
                           cudaStream_t stream) {
@@ -164,12 +291,16 @@ extern "C" int llmie_grouped_gemm_nt(const void* A, long long lda, long long a_g
   if (in_dtype == LLMIE_F32)
     rc = dual ? launch_grouped<float, float, true>(p, tiles, tiles, gz, small, stream)
               : launch_grouped<float, float, false>(p, tiles, tiles, gz, small, stream);
-  else if (out_dtype == LLMIE_F32)
-    rc = dual ? launch_grouped<__nv_bfloat16, float, true>(p, tiles, tiles, gz, small, stream)
-              : launch_grouped<__nv_bfloat16, float, false>(p, tiles, tiles, gz, small, stream);
-  else
-    rc = dual ? launch_grouped<__nv_bfloat16, __nv_bfloat16, true>(p, tiles, tiles, gz, small, stream)
-              : launch_grouped<__nv_bfloat16, __nv_bfloat16, false>(p, tiles, tiles, gz, small, stream);
+  else {
+    const int vec = K % 8 == 0 && lda % 8 == 0 && a_gcs % 8 == 0 && ldw % 8 == 0 && w_gs % 8 == 0 && aligned16(A) &&
+                    aligned16(W);
+    if (out_dtype == LLMIE_F32)
+      rc = dual ? launch_grouped_mma<float, true>(p, tiles, gz, small, vec, stream)
+                : launch_grouped_mma<float, false>(p, tiles, gz, small, vec, stream);
+    else
+      rc = dual ? launch_grouped_mma<__nv_bfloat16, true>(p, tiles, gz, small, vec, stream)
+                : launch_grouped_mma<__nv_bfloat16, false>(p, tiles, gz, small, vec, stream);
+  }
   if (rc != LLMIE_OK) return rc;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;

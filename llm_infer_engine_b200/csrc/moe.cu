@@ -1,7 +1,7 @@
 // The bookkeeping of a routed feed-forward (a mixture of experts); the experts' products themselves are the routed
 // form of grouped_gemm.cu.
 //
-//   route     z = W_r x + b in float32 (a warp per token, each lane a fixed share of the columns, so a token's logits do
+//   route     z = W_r x + b in float32 (a block per token, each lane a fixed share of the columns, so a token's logits do
 //             not depend on the batch); the `top` largest logits are chosen (ties: the lower index), their weights are
 //             the softmax over the chosen logits alone
 //   sort      the (token, choice) pairs grouped by expert into tiles of `tile` positions, padded per expert; one block,
@@ -18,21 +18,34 @@ template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                  int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int d, int n_experts, int top) {
-  extern __shared__ float z_all[];                 // [kRouteWarps][n_experts]
+  // A block per token: the token's row is staged once as float32, its warps share out the experts, and a warp's lanes
+  // take fixed columns of a dot product (four running sums each, added in a fixed order).
+  extern __shared__ float route_smem[];            // [d] the row | [n_experts] the logits
+  float* xs = route_smem;
+  float* z = route_smem + d;
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  if (t >= n_tokens) return;
-  float* z = z_all + warp * n_experts;
+  const int t = blockIdx.x;
   const T* xr = x + (size_t)t * d;
-  for (int e = 0; e < n_experts; ++e) {
+  for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = to_f32(xr[i]);
+  __syncthreads();
+  for (int e = warp; e < n_experts; e += kRouteWarps) {
     const float* wr = w + (size_t)e * d;
-    float s = 0.f;
-    for (int i = lane; i < d; i += 32) s = fmaf(to_f32(xr[i]), wr[i], s);
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int i = lane;
+    for (; i + 96 < d; i += 128) {
+      a0 = fmaf(xs[i], wr[i], a0);
+      a1 = fmaf(xs[i + 32], wr[i + 32], a1);
+      a2 = fmaf(xs[i + 64], wr[i + 64], a2);
+      a3 = fmaf(xs[i + 96], wr[i + 96], a3);
+    }
+    for (; i < d; i += 32) a0 = fmaf(xs[i], wr[i], a0);
+    const float sum = warp_sum((a0 + a1) + (a2 + a3));
+    if (lane == 0) z[e] = sum + (bias ? bias[e] : 0.f);
   }
+  __syncthreads();
+  if (warp != 0) return;
   __syncwarp();
   float first = 0.f, denom = 0.f, mine = 0.f;      // lane k keeps the k-th chosen logit
   int mine_id = 0;
@@ -136,10 +149,10 @@ extern "C" int llmie_moe_route(const void* x, int x_dtype, const float* w, const
                                int n_tokens, int d, int n_experts, int top, cudaStream_t stream) {
   if (n_tokens < 0 || d <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return LLMIE_ERR_BAD_ARG;
   if (x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
-  const size_t smem = (size_t)kRouteWarps * n_experts * sizeof(float);
+  const size_t smem = ((size_t)d + n_experts) * sizeof(float);
   if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_tokens == 0) return LLMIE_OK;
-  const int blocks = (n_tokens + kRouteWarps - 1) / kRouteWarps;
+  const int blocks = n_tokens;
   if (x_dtype == LLMIE_F32)
     launch_k(moe_route_kernel<float>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const float*)x, w, bias, ids, weights, n_tokens, d, n_experts, top);
   else

@@ -59,8 +59,6 @@ class KernelPlan:
         scale, window = options.scale, options.window
         if kv.v.shape[-1] != head_dim or not kv.v.is_contiguous():
             return False
-        if options.scored:
-            return False       # a cap, a bias by distance or a learned sink: kernels that know them are chosen above
         if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16):
             # the tensor-core kernels load the gate 16 bytes at a time: rows that do not start on 16 bytes are
             # applied by a kernel of their own afterwards
@@ -76,8 +74,12 @@ class KernelPlan:
             counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
             ops.attention_decode_mma(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
                                      n_q, n_kv, head_dim, scale, window, pages, n_runs, counters=counters,
-                                     keep_first=options.keep_first, sink=options.sink, gate=gate)
+                                     keep_first=options.keep_first, sink=options.sink, gate=gate,
+                                     softcap=options.softcap, dist_bias=options.distance_bias,
+                                     sink_values=options.sink_values)
             return True
+        if options.scored:
+            return False       # a cap, a bias by distance or a learned sink: the kernels below do not know them
         if ctx.decode and options.plain and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
             n_runs = (ctx.max_kv_len + run - 1) // run

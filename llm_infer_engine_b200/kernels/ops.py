@@ -546,7 +546,9 @@ def attention_decode_mma_pages(n_seqs: int, n_q: int, n_kv: int, max_kv_len: int
 def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table, page_size: int, n_q: int,
                          n_kv: int, head_dim: int, scale: float, window: int, pages_per_run: int, n_runs: int,
                          counters: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None,
-                         keep_first: int = 0, sink: bool = False, gate: Optional[torch.Tensor] = None):
+                         keep_first: int = 0, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                         softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
+                         sink_values: Optional[torch.Tensor] = None):
     """Attention for a one-token step on the tensor cores (bfloat16): a warp per cache page, the warps of a
     block merged in shared memory. Arguments as attention_decode; n_runs * pages_per_run pages must cover
     the longest sequence. With n_runs == 1 neither scratch nor counters are touched. keep_first, sink and gate
@@ -576,12 +578,20 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
         base, n_ml, cptr = scratch.data_ptr(), n * n_q * n_runs, counters.data_ptr()
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_decode_mma", "llmie_attention_decode_mma_ex",
-            [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 5 + [_c_void_p, _c_int, _c_void_p])
+            [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 5 + [_c_void_p, _c_int, _c_float, _c_void_p,
+                                                                            _c_int, _c_void_p, _c_void_p])
+    bias_len = 0
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32, (n_q, None))
+        bias_len = dist_bias.shape[1]
+    if sink_values is not None:
+        _need(sink_values, "sink_values", torch.float32, (n_q,))
+        sink = True
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base or None,
              (base + 4 * n_ml) or None, (base + 8 * n_ml) or None, cptr, seq_slot.data_ptr(), seq_kvlen.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale),
              int(window), int(pages_per_run), int(n_runs), int(keep_first), 1 if sink else 0, _ptr(gate), gate_ld,
-             _stream()), "attention_decode_mma")
+             float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _stream()), "attention_decode_mma")
     return out
 
 

@@ -44,12 +44,12 @@ TINY_B = {"architecture": "Dofipel", "vocab": 97, "width": 100, "logit_scale": 1
 # C: head sizes 64 and 128 with equal value sizes (what the tensor-core attention kernels take) and a wider latent.
 TINY_C = {"architecture": "Dofipel", "vocab": 160, "width": 128, "logit_scale": 0.25, "norm": {"eps": 1e-6}, "layers": [
     {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 100}, "scale": 0.125,
-                                    "softcap": 30.0, "bias_max": 200}, "mlp": {"kind": "dense", "ff": 256}},
+                                    "softcap": 5.0, "bias_max": 200}, "mlp": {"kind": "dense", "ff": 256}},
     {"type": "latent_attention", "mixer": {"heads": 4, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "scale": 0.15,
                                            "rot": {"base": 100000.0, "dims": 16}},
      "mlp": {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 64}, "shared": {"ff": 64}}},
     {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 128, "mask": {"size": 65}, "scale": 0.09,
-                                    "softcap": 15.0, "bias_max": 100}, "mlp": {"kind": "dense", "ff": 128}},
+                                    "softcap": 3.0, "bias_max": 100}, "mlp": {"kind": "dense", "ff": 128}},
     {"type": "latent_attention", "mixer": {"heads": 2, "dim": 64, "rot_dim": 16, "vdim": 64, "kv_rank": 64, "scale": 0.1,
                                            "rot": {"base": 100000.0, "dims": 16}, "kv_from": 1},
      "mlp": {"kind": "dense", "ff": 64}}]}
