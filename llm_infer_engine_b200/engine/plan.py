@@ -58,7 +58,8 @@ class KernelPlan:
         window. A value head size that differs from the key head size is the plain kernel's alone."""
         scale, window = options.scale, options.window
         if kv.v.shape[-1] != head_dim or not kv.v.is_contiguous():
-            return False
+            # a value size of its own, or values that are columns of the key rows (a latent)
+            return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
         if gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16):
             # the tensor-core kernels load the gate 16 bytes at a time: rows that do not start on 16 bytes are
             # applied by a kernel of their own afterwards
@@ -79,7 +80,8 @@ class KernelPlan:
                                      sink_values=options.sink_values)
             return True
         if options.scored:
-            return False       # a cap, a bias by distance or a learned sink: the kernels below do not know them
+            # a cap, a bias by distance or a learned sink: the kernels below do not know them
+            return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
         if ctx.decode and options.plain and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
             n_runs = (ctx.max_kv_len + run - 1) // run
@@ -95,3 +97,17 @@ class KernelPlan:
                                      options.keep_first, options.sink, gate)
             return True
         return False
+
+    def _attention_by_rows(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
+        """The tensor-core kernel whose rows are the (token, head) pairs of a key/value head: prompts and one-token
+        steps of the shapes and options the kernels above do not take. It knows no kept first keys."""
+        shared_rows = not kv.v.is_contiguous()
+        if options.keep_first or not ops.attention_rows_mma_supported(head_dim, kv.v.shape[-1], kv.page_size, q.dtype,
+                                                                      shared_rows):
+            return False
+        ops.attention_rows_mma(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table, kv.page_size,
+                               ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, options.scale, options.window,
+                               options.softcap, options.distance_bias, options.sink_values, options.sink)
+        if gate is not None:
+            ops.sigmoid_gate(out, gate)
+        return True

@@ -38,6 +38,7 @@ FAMILIES: Dict[str, tuple] = {
     "attention_decode": ("attention_decode.cu", [], []),
     "attention_decode_mma": ("attention_decode_mma.cu", [], []),
     "attention_prefill_tc": ("attention_prefill_tc.cu", [], []),
+    "attention_rows_mma": ("attention_rows_mma.cu", [], []),
     "gemm_simt": ("gemm_simt.cu", [], []),
     "gemm_skinny": ("gemm_skinny.cu", [], []),
     "gemm_tc": ("gemm_tc.cu", [], []),

@@ -1273,3 +1273,59 @@ def latent_prepare(proj, q_off: int, dkv_off: int, q_out, cache, norm_w, eps: fl
              tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              page_size, T, n_heads, dim, rot, rank, 1 if write else 0, _dt(proj, "proj"), _stream()), "latent_prepare")
     return q_out
+
+
+# ------------------------------------------------------------------------------------------ attention by rows
+def attention_rows_mma_supported(head_dim: int, v_head_dim: int, page_size: int, dtype: torch.dtype,
+                                 shared_rows: bool) -> bool:
+    """The sizes attention_rows_mma.cu takes (answered without loading the library): bfloat16, a head size that is a
+    multiple of 16 up to 1024, a value size that is a multiple of 8 up to 512, pages of whole tiles of 32 keys, and
+    about 200 KB of shared memory for the staged tiles."""
+    if dtype != torch.bfloat16 or head_dim <= 0 or head_dim % 16 or head_dim > 1024 or v_head_dim <= 0 \
+            or v_head_dim % 8 or v_head_dim > 512 or page_size % 32 or (shared_rows and v_head_dim > head_dim):
+        return False
+    kp, vp = head_dim + 8, v_head_dim + 8
+    smem = 32 * kp * 2 + 2 * 32 * kp * 2 + (0 if shared_rows else 2 * 32 * vp * 2) + 32 * 33 * 4 + 32 * 40 * 2 + 32 * 4
+    return smem <= 200 * 1024
+
+
+def attention_rows_mma(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, page_size: int, n_seqs: int,
+                       max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
+                       softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
+                       sink_values: Optional[torch.Tensor] = None, sink: bool = False):
+    """Attention on the tensor cores with the (token, head) pairs of a key/value head as rows (bfloat16): prompts and
+    one-token steps, any head size that is a multiple of 16, a value size of its own, values that are columns of the
+    key rows (v_cache a view into k_cache), scale, window, cap, bias by distance and sink as in attention_paged."""
+    T = q.shape[0]
+    hdv = v_cache.shape[-1]
+    _need(q, "q", torch.bfloat16, (T, n_q * head_dim))
+    _need(out, "out", torch.bfloat16, (T, n_q * hdv))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
+    shared_rows = False
+    if v_cache.is_contiguous():
+        _need(v_cache, "v_cache", torch.bfloat16, (k_cache.shape[0], n_kv, page_size, hdv))
+        v_ld = hdv
+    else:
+        v_ld = v_cache.stride(-2)
+        if (v_cache.dtype is not torch.bfloat16 or tuple(v_cache.shape) != (k_cache.shape[0], n_kv, page_size, hdv)
+                or v_cache.stride() != (n_kv * page_size * v_ld, page_size * v_ld, v_ld, 1)):
+            raise KernelError("attention_rows_mma: v_cache must be contiguous or a column range of contiguous rows")
+        shared_rows = v_cache.data_ptr() == k_cache.data_ptr() and v_ld == head_dim
+    for name, t in (("cu_q", cu_q), ("seq_slot", seq_slot), ("seq_start", seq_start), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    bias_len = 0
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32, (n_q, None))
+        bias_len = dist_bias.shape[1]
+    if sink_values is not None:
+        _need(sink_values, "sink_values", torch.float32, (n_q,))
+        sink = True
+    _work(2 * _nbytes(q) + 1.0 * STEP_HINT["kv_total"] * n_kv * (head_dim + (0 if shared_rows else hdv)) * 2,
+          2.0 * n_q * (head_dim + hdv) * STEP_HINT["pairs"])
+    f = _fn("attention_rows_mma", "llmie_attention_rows_mma",
+            [_c_void_p] * 8 + [_c_int] * 10 + [_c_float, _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+    _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
+             seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n_seqs, max_q_len, n_q, n_kv,
+             head_dim, hdv, int(v_ld), 1 if shared_rows else 0, float(scale), int(window), float(softcap or 0.0),
+             _ptr(dist_bias), bias_len, _ptr(sink_values), 1 if sink else 0, _stream()), "attention_rows_mma")
+    return out
