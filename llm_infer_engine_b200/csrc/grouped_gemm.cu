@@ -185,19 +185,45 @@ grouped_gemm_mma_kernel(const GroupedArgs p, const int vec) {
     return *reinterpret_cast<const uint4*>(e);
   };
 
-  for (int k0 = 0; k0 < p.K; k0 += BK) {
-    for (int c = tid; c < BM * CH; c += 128) {
-      const int r = c / CH, kc = (c % CH) * 8;
-      const int ra = rowA[r];
-      *reinterpret_cast<uint4*>(&As[r][kc]) = fetch(A + (size_t)(ra < 0 ? 0 : ra) * p.lda, ra >= 0, k0 + kc);
+  // The next K step's pieces are requested into registers before this step's products, so that the loads are in flight
+  // while the tensor cores work: with few rows a group the weights' stream is all there is to wait for.
+  constexpr int A_PER = BM * CH / 128 > 0 ? BM * CH / 128 : 1, W_PER = BN * CH / 128;
+  static_assert((BM * CH) % 128 == 0 || BM * CH < 128, "whole rounds of the block's threads");
+  uint4 ra[A_PER], rw[NW][W_PER];
+  auto request = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < A_PER; ++j) {
+      const int c = tid + j * 128;
+      if (c < BM * CH) {
+        const int r = c / CH, kc = (c % CH) * 8;
+        const int row = rowA[r];
+        ra[j] = fetch(A + (size_t)(row < 0 ? 0 : row) * p.lda, row >= 0, k0 + kc);
+      }
     }
-    for (int c = tid; c < BN * CH; c += 128) {
+#pragma unroll
+    for (int j = 0; j < W_PER; ++j) {
+      const int c = tid + j * 128;
       const int r = c / CH, kc = (c % CH) * 8;
       const int gn = n0 + r;
-      *reinterpret_cast<uint4*>(&Ws[0][r][kc]) = fetch(W + (size_t)gn * p.ldw, gn < p.N, k0 + kc);
-      if (DUAL) *reinterpret_cast<uint4*>(&Ws[NW - 1][r][kc]) = fetch(W + (size_t)(gn + p.N) * p.ldw, gn < p.N, k0 + kc);
+      rw[0][j] = fetch(W + (size_t)gn * p.ldw, gn < p.N, k0 + kc);
+      if (DUAL) rw[NW - 1][j] = fetch(W + (size_t)(gn + p.N) * p.ldw, gn < p.N, k0 + kc);
+    }
+  };
+  request(0);
+  for (int k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < A_PER; ++j) {
+      const int c = tid + j * 128;
+      if (c < BM * CH) *reinterpret_cast<uint4*>(&As[c / CH][(c % CH) * 8]) = ra[j];
+    }
+#pragma unroll
+    for (int j = 0; j < W_PER; ++j) {
+      const int c = tid + j * 128;
+      *reinterpret_cast<uint4*>(&Ws[0][c / CH][(c % CH) * 8]) = rw[0][j];
+      if (DUAL) *reinterpret_cast<uint4*>(&Ws[NW - 1][c / CH][(c % CH) * 8]) = rw[NW - 1][j];
     }
     __syncthreads();
+    if (k0 + BK < p.K) request(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       const unsigned a0 = *reinterpret_cast<const unsigned*>(&As[row0 + g][kk + 2 * t]);

@@ -84,7 +84,8 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
 
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int top, int n_experts, int tile, int max_tiles,
-                int* __restrict__ sorted_token, int* __restrict__ sorted_pair, int* __restrict__ tile_group) {
+                int* __restrict__ sorted_token, int* __restrict__ sorted_pair, int* __restrict__ tile_group,
+                int* __restrict__ group_end, int* __restrict__ pair_pos) {
   extern __shared__ int sm[];                      // counts | offsets | cursor, n_experts each
   int* counts = sm;
   int* offsets = sm + n_experts;
@@ -113,19 +114,39 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int top, int n_experts
   for (int e = tid; e < n_experts; e += nt) {
     const int t0 = offsets[e] / tile, n = (counts[e] + tile - 1) / tile;
     for (int j = 0; j < n && t0 + j < max_tiles; ++j) tile_group[t0 + j] = e;
+    if (group_end) group_end[e] = offsets[e] + n * tile;      // where the expert's positions end, padding included
   }
   for (int i = tid; i < n_pairs; i += nt) {
     const int e = ids[i];
     if (e < 0 || e >= n_experts) continue;
     const int pos = offsets[e] + atomicAdd(&cursor[e], 1);
     if (pos < cap) { sorted_pair[pos] = i; sorted_token[pos] = i / top; }
+    if (pair_pos) pair_pos[i] = pos < cap ? pos : 0;
   }
 }
 
-template <typename TS>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
-                                   const TS* __restrict__ shared_out, float* __restrict__ out, int d, int top,
-                                   size_t total) {
+// out[p] = x[rows[p]] (zeros where rows[p] < 0): the tokens in the order of their experts, for a library product that
+// wants each expert's rows side by side. d % 8 == 0, 16-byte aligned.
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
+                                       __nv_bfloat16* __restrict__ out, int d8, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t pos = i / d8;
+    const int c = (int)(i - pos * d8);
+    const int r = rows[pos];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r >= 0) v = reinterpret_cast<const uint4*>(x)[(size_t)r * d8 + c];
+    reinterpret_cast<uint4*>(out)[i] = v;
+  }
+}
+
+template <typename TS, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pair_pos,
+                                   const float* __restrict__ weights, const TS* __restrict__ shared_out,
+                                   float* __restrict__ out, int d, int top, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -134,7 +155,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     const size_t t = i / d;
     const int c = (int)(i - t * d);
     float s = 0.f;
-    for (int k = 0; k < top; ++k) s = fmaf(weights[t * top + k], y[(t * top + k) * d + c], s);
+    for (int k = 0; k < top; ++k) {
+      const size_t row = pair_pos ? (size_t)pair_pos[t * top + k] : t * top + k;
+      s = fmaf(weights[t * top + k], to_f32(y[row * d + c]), s);
+    }
     if (shared_out) s += to_f32(shared_out[i]);
     out[i] = s;
   }
@@ -164,30 +188,53 @@ extern "C" int llmie_moe_route(const void* x, int x_dtype, const float* w, const
 // ids int32 [n_pairs] (pair = token * top + choice); sorted_token, sorted_pair int32 [max_tiles * tile];
 // tile_group int32 [max_tiles]. max_tiles must be at least n_pairs / tile + min(n_pairs, n_experts).
 extern "C" int llmie_moe_sort(const int* ids, int n_pairs, int top, int n_experts, int tile, int max_tiles,
-                              int* sorted_token, int* sorted_pair, int* tile_group, cudaStream_t stream) {
+                              int* sorted_token, int* sorted_pair, int* tile_group, int* group_end, int* pair_pos,
+                              cudaStream_t stream) {
   if (n_pairs < 0 || top <= 0 || n_experts <= 0 || tile <= 0 || max_tiles <= 0) return LLMIE_ERR_BAD_ARG;
   const int need = n_pairs / tile + (n_pairs < n_experts ? n_pairs : n_experts);
   if (max_tiles < need) return LLMIE_ERR_BAD_ARG;
   const size_t smem = (size_t)3 * n_experts * sizeof(int);
   if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  launch_k(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, top, n_experts, tile, max_tiles, sorted_token, sorted_pair, tile_group);
+  launch_k(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, top, n_experts, tile, max_tiles, sorted_token, sorted_pair, tile_group, group_end, pair_pos);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
 
-// y float32 [T * top, d]; weights float32 [T, top]; shared_out [T, d] of shared_dtype or null; out float32 [T, d].
-extern "C" int llmie_moe_combine(const float* y, const float* weights, const void* shared_out, int shared_dtype,
-                                 float* out, int n_tokens, int d, int top, cudaStream_t stream) {
+// y [rows, d] float32 or bfloat16; row of pair i = pair_pos[i] (int32 [T * top]) or i itself when pair_pos is null;
+// weights float32 [T, top]; shared_out [T, d] of shared_dtype or null; out float32 [T, d].
+extern "C" int llmie_moe_combine(const void* y, int y_dtype, const int* pair_pos, const float* weights,
+                                 const void* shared_out, int shared_dtype, float* out, int n_tokens, int d, int top,
+                                 cudaStream_t stream) {
   if (n_tokens < 0 || d <= 0 || top <= 0) return LLMIE_ERR_BAD_ARG;
-  if (shared_out && shared_dtype != LLMIE_F32 && shared_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
+  if ((shared_out && shared_dtype != LLMIE_F32 && shared_dtype != LLMIE_BF16) || (y_dtype != LLMIE_F32 && y_dtype != LLMIE_BF16))
+    return LLMIE_ERR_DTYPE;
   if (n_tokens == 0) return LLMIE_OK;
   const size_t total = (size_t)n_tokens * d;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (shared_out && shared_dtype == LLMIE_BF16)
-    launch_k(moe_combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, weights, (const __nv_bfloat16*)shared_out, out, d, top, total);
-  else
-    launch_k(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, weights, (const float*)shared_out, out, d, top, total);
+  const bool sb = shared_out && shared_dtype == LLMIE_BF16;
+  const dim3 grid((unsigned)blocks), block(256);
+  if (y_dtype == LLMIE_F32) {
+    if (sb) launch_k(moe_combine_kernel<__nv_bfloat16, float>, grid, block, 0, stream, (const float*)y, pair_pos, weights, (const __nv_bfloat16*)shared_out, out, d, top, total);
+    else launch_k(moe_combine_kernel<float, float>, grid, block, 0, stream, (const float*)y, pair_pos, weights, (const float*)shared_out, out, d, top, total);
+  } else {
+    if (sb) launch_k(moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)y, pair_pos, weights, (const __nv_bfloat16*)shared_out, out, d, top, total);
+    else launch_k(moe_combine_kernel<float, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)y, pair_pos, weights, (const float*)shared_out, out, d, top, total);
+  }
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// out [n_positions, d] = x[rows[p]] (zero rows where rows[p] < 0); bfloat16, d % 8 == 0, both 16-byte aligned.
+extern "C" int llmie_moe_gather_rows(const void* x, const int* rows, void* out, int n_positions, int d,
+                                     cudaStream_t stream) {
+  if (n_positions < 0 || d <= 0 || d % 8) return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(x) || !aligned16(out)) return LLMIE_ERR_ALIGNMENT;
+  if (n_positions == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_positions * (d / 8);
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_k(moe_gather_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, d / 8, total);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

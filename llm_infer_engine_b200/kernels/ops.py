@@ -1212,37 +1212,81 @@ def moe_max_tiles(n_pairs: int, n_experts: int, tile: int) -> int:
     return n_pairs // tile + min(n_pairs, n_experts)
 
 
-def moe_sort(ids, n_experts: int, tile: int, sorted_token, sorted_pair, tile_group):
+def moe_sort(ids, n_experts: int, tile: int, sorted_token, sorted_pair, tile_group, group_end=None, pair_pos=None):
     """Groups the (token, choice) pairs of ids int32 [T, top] by expert into tiles of `tile` positions: sorted_pair[p]
     = token * top + choice at position p, sorted_token[p] = token, -1 = padding; tile_group[i] = expert of tile i, -1 =
-    unused. The arrays are sized for moe_max_tiles."""
+    unused. The arrays are sized for moe_max_tiles. Optional: group_end int32 [E] receives where each expert's
+    positions end (padding included), pair_pos int32 [T * top] the position of every pair."""
     T, top = ids.shape
     n_tiles = tile_group.shape[0]
     _need(ids, "ids", torch.int32)
     _need(tile_group, "tile_group", torch.int32, (n_tiles,))
     _need(sorted_token, "sorted_token", torch.int32, (n_tiles * tile,))
     _need(sorted_pair, "sorted_pair", torch.int32, (n_tiles * tile,))
-    f = _fn("moe", "llmie_moe_sort", [_c_void_p] + [_c_int] * 5 + [_c_void_p] * 4)
+    if group_end is not None:
+        _need(group_end, "group_end", torch.int32, (n_experts,))
+    if pair_pos is not None:
+        _need(pair_pos, "pair_pos", torch.int32, (T * top,))
+    f = _fn("moe", "llmie_moe_sort", [_c_void_p] + [_c_int] * 5 + [_c_void_p] * 6)
     _check(f(ids.data_ptr(), T * top, top, n_experts, tile, n_tiles, sorted_token.data_ptr(), sorted_pair.data_ptr(),
-             tile_group.data_ptr(), _stream()), "moe_sort")
+             tile_group.data_ptr(), _ptr(group_end), _ptr(pair_pos), _stream()), "moe_sort")
 
 
-def moe_combine(y, weights, shared_out, out):
-    """out[t] = sum_k weights[t, k] * y[t * top + k] (+ shared_out[t]); y float32 [T * top, d]; out float32 [T, d]."""
+def moe_combine(y, weights, shared_out, out, pair_pos=None):
+    """out[t] = sum_k weights[t, k] * y[row of pair t * top + k] (+ shared_out[t]); the row of a pair is the pair's
+    own number, or pair_pos[pair] when that is given (y then holds the pairs in sorted order). y float32 or bfloat16
+    [rows, d]; out float32 [T, d]."""
     T, top = weights.shape
     d = out.shape[1]
-    _need(y, "y", torch.float32, (T * top, d))
+    _need(y, "y", None, (None if pair_pos is not None else T * top, d))
     _need(weights, "weights", torch.float32)
     _need(out, "out", torch.float32, (T, d))
     if shared_out is not None:
         _need(shared_out, "shared_out", None, (T, d))
-    _work(_nbytes(y, weights, shared_out, out))
-    f = _fn("moe", "llmie_moe_combine", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
-                                         _c_void_p])
-    _check(f(y.data_ptr(), weights.data_ptr(), _ptr(shared_out),
+    if pair_pos is not None:
+        _need(pair_pos, "pair_pos", torch.int32, (T * top,))
+    _work(T * top * d * y.element_size() + _nbytes(weights, shared_out, out))
+    f = _fn("moe", "llmie_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                         _c_int, _c_int, _c_void_p])
+    _check(f(y.data_ptr(), _dt(y, "y"), _ptr(pair_pos), weights.data_ptr(), _ptr(shared_out),
              _dt(shared_out, "shared_out") if shared_out is not None else 0, out.data_ptr(), T, d, top, _stream()),
            "moe_combine")
     return out
+
+
+def moe_gather_rows(x, rows, out):
+    """out[p] = x[rows[p]] (zeros where rows[p] < 0); bfloat16 rows of a multiple of 8 elements."""
+    P, d = out.shape
+    _need(x, "x", torch.bfloat16, (None, d))
+    _need(out, "out", torch.bfloat16)
+    _need(rows, "rows", torch.int32)
+    if rows.shape[0] < P:
+        raise KernelError("moe_gather_rows: rows shorter than the output")
+    _work(2 * _nbytes(out))
+    f = _fn("moe", "llmie_moe_gather_rows", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(x.data_ptr(), rows.data_ptr(), out.data_ptr(), P, d, _stream()), "moe_gather_rows")
+    return out
+
+
+def library_grouped_mm(x: torch.Tensor, w: torch.Tensor, group_end: torch.Tensor) -> torch.Tensor:
+    """Rows [group_end[e-1], group_end[e]) of x [P, K] times w[e]^T (w [E, N, K]) through the library's grouped GEMM
+    (bfloat16 in and out, float32 accumulation); rows beyond group_end[-1] are left as they are. Like `library_mm`
+    this is the product that prompts leave to the vendor library; the offsets stay on the device."""
+    def run():
+        return torch._grouped_mm(x, w.transpose(-2, -1), offs=group_end)
+    t = trace.timer
+    if t is None:
+        return run()
+    P, K = x.shape
+    t.note(_nbytes(x, w) + P * w.shape[1] * 2, 2.0 * P * w.shape[1] * K)
+    return t.run("library_grouped_mm", run, ())
+
+
+def library_grouped_mm_ok(n_pairs: int, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Whether the routed products of a prompt go to the library: bfloat16, enough pairs for tiles of 64 to fill, and
+    rows that start on 16 bytes."""
+    return (hasattr(torch, "_grouped_mm") and w_gate_up.dtype == torch.bfloat16 and n_pairs > GROUPED_SMALL_ROWS * 4
+            and w_gate_up.shape[2] % 8 == 0 and w_down.shape[2] % 8 == 0 and w_down.shape[1] % 8 == 0)
 
 
 # ------------------------------------------------------------------------------------------ latent attention

@@ -10,7 +10,9 @@ With u [T, d] the branch input, E experts of width f, each down_e(act(gate_e u) 
 The (token, choice) pairs are sorted by expert on the device into tiles (no host round trip: array sizes are upper
 bounds, so a captured step replays it), the experts' two products run as ONE routed launch each over stacked weights
 [E, 2 f, d] and [E, d, f] (gate and up fused with the activation), and the pairs are combined per token in the order
-of the choices, in float32. A token's result does not depend on what else is in the batch.
+of the choices, in float32. A token's result does not depend on what else is in the batch. Prompts of a bfloat16 engine
+hand the two products to the vendor library's grouped GEMM instead (as the dense layers hand theirs to its plain one):
+the tokens are gathered into the order of their experts first, the offsets stay on the device.
 """
 from __future__ import annotations
 
@@ -105,6 +107,22 @@ class RoutedExperts(FeedForward):
             index = torch.empty(2 * n_tiles * tile + n_tiles, dtype=torch.int32, device=dev)
             sorted_token, sorted_pair = index[:n_tiles * tile], index[n_tiles * tile:2 * n_tiles * tile]
             tile_group = index[2 * n_tiles * tile:]
+            shared = None
+            if ops.library_grouped_mm_ok(n_pairs, w, self.w_down):
+                # prompts: each expert's rows side by side, the two products by the library's grouped GEMM
+                extra = torch.empty(E + n_pairs, dtype=torch.int32, device=dev)
+                group_end, pair_pos = extra[:E], extra[E:]
+                ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group, group_end, pair_pos)
+                xs = ops.moe_gather_rows(xin, sorted_token, torch.empty((n_tiles * tile, self.hidden), dtype=w.dtype,
+                                                                         device=dev))
+                gu = ops.library_grouped_mm(xs, w, group_end)
+                act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
+                ops.gated_act(gu, act, self.activation)
+                y = ops.library_grouped_mm(act, self.w_down, group_end)
+                if self.shared is not None:
+                    shared = self.shared.forward(x, ctx)
+                out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+                return ops.moe_combine(y, weights, shared, out, pair_pos)
             ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group)
             # gate and up of every pair's expert with the activation; rows stay in sorted order
             act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
