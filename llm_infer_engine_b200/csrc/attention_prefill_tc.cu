@@ -108,14 +108,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
-__global__ void __maxnreg__(AttnCfg<HD>::kMaxRegs)
+// Options that change single scores, each off at 0 / null (kernels instantiated with SCORED = false never look at
+// them): softcap c > 0 turns a scaled score s into c * tanh(s / c); dist_bias (float32 [n_q, bias_len]) adds a number per
+// query head and distance (query position - key position; bias_len - 1 and more share the last entry) after the cap,
+// unscaled; sink_vals (float32 [n_q]) is the sink's score per head instead of 0.
+struct ScoreOptions {
+  float softcap;
+  const float* dist_bias;
+  int bias_len;
+  const float* sink_vals;
+};
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD, bool SCORED>
+__global__ void __maxnreg__(SCORED && HD == 64 ? 96 : AttnCfg<HD>::kMaxRegs)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, const int* __restrict__ block_table, int max_pages,
                             int scratch_page, int n_q, int n_kv, float scale, int window, int keep_first, int sink,
-                            const __nv_bfloat16* __restrict__ gate, int gate_ld, int* __restrict__ status) {
+                            const __nv_bfloat16* __restrict__ gate, int gate_ld, int* __restrict__ status,
+                            const ScoreOptions so) {
   using Cfg = AttnCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
@@ -358,7 +376,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
-        if (edge) {
+        if (SCORED) {
+          // The cap and the bias by distance change every score of every tile: they are applied here, once, and the
+          // changed scores written back to tensor memory in the units the second pass expects (score / scale), with
+          // -inf where this row may not look (as the branch below does for edge tiles).
+          const unsigned span = (unsigned)(qpos - lo);
+          const int kept_rel = min(keep_first, qpos + 1) - kbase;
+          const float* brow = so.dist_bias ? so.dist_bias + (size_t)head * so.bias_len : nullptr;
+          const float inv_cap = so.softcap > 0.f ? 1.f / so.softcap : 0.f;
+          const float inv_scale = 1.f / scale;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[i]) * scale;
+            if (so.softcap > 0.f) x = so.softcap * tanh_approx(x * inv_cap);
+            if (brow) x += __ldg(brow + min(max(qpos - (kbase + c0 + i), 0), so.bias_len - 1));
+            v[i] = __float_as_uint(x * inv_scale);
+            if (edge && (unsigned)(c0 + i - lo_rel) > span && c0 + i >= kept_rel) v[i] = 0xff800000u;
+            mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
+          }
+          tmem_st_32x32(lane_addr + b * 128 + half * kCols + c0, v);
+        } else if (edge) {
           // A tile that the causal line or the window's far end crosses: the scores this row may not see become
           // -inf here, in tensor memory too, so that the second pass is the same for every tile (2^-inf = 0).
           // Column c of this thread's half is seen if lo <= kbase + c <= qpos (one unsigned comparison), or if
@@ -376,7 +413,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
         }
       }
-      if (edge) tmem_st_wait();
+      if (edge || SCORED) tmem_st_wait();
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       float other;
       if (!__all_sync(0xffffffffu, exchange(m_tile, other))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
@@ -451,7 +488,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok && r < rows_here) {
       // the sink: one more term exp(0 - max) in the denominator (it has no value, the numerator stays);
       // a maximum far below zero makes the term infinite and the output zero, which is the limit
-      if (sink) l_run += exp2_approx(-m_run * sl2);
+      if (sink) {
+        const float sv = (SCORED && so.sink_vals) ? so.sink_vals[head] * 1.4426950408889634f : 0.f;
+        l_run += exp2_approx(sv - m_run * sl2);
+      }
       const float inv = 1.f / l_run;
       const size_t row_off = ((size_t)(q_begin + t0 + r) * n_q + head) * HD + half * kOut;
       __nv_bfloat16* dst = out + row_off;
@@ -480,12 +520,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
-template <int HD>
+template <int HD, bool SCORED>
 static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q,
                           const int* seq_slot, const int* seq_start, const int* block_table, int max_pages,
                           int n_pages_total, int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, float scale,
                           int window, int keep_first, int sink, const void* gate, int gate_ld, int* status,
-                          cudaStream_t stream) {
+                          const ScoreOptions so, cudaStream_t stream) {
   using Cfg = AttnCfg<HD>;
   CUtensorMap map_q, map_k, map_v;
   int rc = tc::make_tmap_bf16_2d(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_q * HD, (uint64_t)n_q * HD, kQTile);
@@ -495,13 +535,13 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
   if (rc != LLMIE_OK) return rc;
   rc = tc::make_tmap_bf16_2d(&map_v, v_cache, kv_rows, HD, HD, 64);
   if (rc != LLMIE_OK) return rc;
-  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SCORED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::kSmem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_q, (max_q_len + kQTile - 1) / kQTile, n_seqs);
-  attention_prefill_tc_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
+  attention_prefill_tc_kernel<HD, SCORED><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
       map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total - 1,
-      n_q, n_kv, scale, window, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, status);
+      n_q, n_kv, scale, window, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, status, so);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -521,26 +561,50 @@ extern "C" int llmie_attention_prefill_tc_supported(int hd, int page_size) {
 // scale must be positive. Options, each off at 0 / null: keep_first (with a window: the first keys of a sequence stay
 // visible behind it), sink (one more softmax term of score 0 without a value), gate (bfloat16 rows of n_q * hd
 // elements, gate_ld apart, 16-byte aligned: the output is multiplied by sigmoid(gate)).
+static int prefill_tc_entry(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q,
+                            const int* seq_slot, const int* seq_start, const int* block_table, int max_pages,
+                            int n_pages_total, int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, int hd,
+                            float scale, int window, int keep_first, int sink, const void* gate, int gate_ld, int* status,
+                            const ScoreOptions so, cudaStream_t stream) {
+  if (n_tokens < 0 || n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || n_pages_total <= 0)
+    return LLMIE_ERR_BAD_ARG;
+  if (keep_first < 0 || (gate && (gate_ld < n_q * hd || gate_ld % 8 || !aligned16(gate)))) return LLMIE_ERR_BAD_ARG;
+  if (!(scale > 0.f)) return LLMIE_ERR_BAD_ARG;   // the running maximum is taken before the scores are scaled
+  if (so.softcap < 0.f || (so.dist_bias && so.bias_len <= 0) || (so.sink_vals && !sink)) return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+  if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
+  if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const bool scored = so.softcap > 0.f || so.dist_bias || so.sink_vals;
+#define LLMIE_PREFILL_ARGS                                                                                            \
+  q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total, n_tokens, n_seqs,       \
+      max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate, gate_ld, status, so, stream
+  if (hd == 64) return scored ? launch_prefill<64, true>(LLMIE_PREFILL_ARGS) : launch_prefill<64, false>(LLMIE_PREFILL_ARGS);
+  if (hd == 128) return scored ? launch_prefill<128, true>(LLMIE_PREFILL_ARGS) : launch_prefill<128, false>(LLMIE_PREFILL_ARGS);
+#undef LLMIE_PREFILL_ARGS
+  return LLMIE_ERR_UNSUPPORTED_SIZE;
+}
+
 extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* cu_q, const int* seq_slot, const int* seq_start,
                                           const int* block_table, int max_pages, int n_pages_total, int n_tokens,
                                           int n_seqs, int max_q_len, int n_q, int n_kv, int hd, float scale, int window,
                                           int keep_first, int sink, const void* gate, int gate_ld, int* status,
                                           cudaStream_t stream) {
-  if (n_tokens < 0 || n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || n_pages_total <= 0)
-    return LLMIE_ERR_BAD_ARG;
-  if (keep_first < 0 || (gate && (gate_ld < n_q * hd || gate_ld % 8 || !aligned16(gate)))) return LLMIE_ERR_BAD_ARG;
-  if (!(scale > 0.f)) return LLMIE_ERR_BAD_ARG;   // the running maximum is taken before the scores are scaled
-  if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
-  if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
-  if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (hd == 64)
-    return launch_prefill<64>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
-                              n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate,
-                              gate_ld, status, stream);
-  if (hd == 128)
-    return launch_prefill<128>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
-                               n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate,
-                              gate_ld, status, stream);
-  return LLMIE_ERR_UNSUPPORTED_SIZE;
+  return prefill_tc_entry(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total,
+                          n_tokens, n_seqs, max_q_len, n_q, n_kv, hd, scale, window, keep_first, sink, gate, gate_ld,
+                          status, ScoreOptions{0.f, nullptr, 0, nullptr}, stream);
+}
+
+// The same with the options that change single scores (see ScoreOptions): a cap, a bias by distance, the sink's score
+// per head.
+extern "C" int llmie_attention_prefill_tc_scored(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                 const int* cu_q, const int* seq_slot, const int* seq_start,
+                                                 const int* block_table, int max_pages, int n_pages_total, int n_tokens,
+                                                 int n_seqs, int max_q_len, int n_q, int n_kv, int hd, float scale,
+                                                 int window, int keep_first, int sink, const void* gate, int gate_ld,
+                                                 int* status, float softcap, const float* dist_bias, int bias_len,
+                                                 const float* sink_vals, cudaStream_t stream) {
+  return prefill_tc_entry(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total,
+                          n_tokens, n_seqs, max_q_len, n_q, n_kv, hd, scale, window, keep_first, sink, gate, gate_ld,
+                          status, ScoreOptions{softcap, dist_bias, bias_len, sink_vals}, stream);
 }

@@ -178,8 +178,9 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         gate += red[w][nb][j][col];
         up += red[w][nb][j + 8][col];
       }
-      const float act = gate / (1.f + expf(-gate)) * up;
-      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + j] = __float2bfloat16_rn(act);
+      // act 0: silu, the form this epilogue began with; any other activation code is applied to the gate instead
+      const float gated = (act ? apply_act(gate, act) : gate / (1.f + expf(-gate))) * up;
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + j] = __float2bfloat16_rn(gated);
     }
   } else {
     for (int idx = threadIdx.x; idx < NB * 128; idx += WARPS * 32) {
@@ -280,6 +281,14 @@ extern "C" int llmie_gemm_skinny(const void* x, const void* W, void* out, int ba
                                  int epilogue, cudaStream_t stream) {
   if (epilogue == kBiasAct) return LLMIE_ERR_BAD_ARG;
   return gemm_skinny_entry(x, W, out, batch, N, K, ldo, epilogue, nullptr, 0, stream);
+}
+
+// out bfloat16 [batch, N / 2] = act(x Wg^T) * (x Wu^T) for W = [gate rows; up rows]: epilogue 3 with an activation of
+// the caller's choice (a code of common.cuh's apply_act; 0 = silu).
+extern "C" int llmie_gemm_skinny_gated(const void* x, const void* W, void* out, int batch, int N, int K, int ldo, int act,
+                                       cudaStream_t stream) {
+  if (act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
+  return gemm_skinny_entry(x, W, out, batch, N, K, ldo, kSwiGLU, nullptr, act == 4 ? 0 : act, stream);
 }
 
 // out bfloat16 [batch, ldo] = act(x W^T + bias) in one kernel.

@@ -12,7 +12,7 @@
 
 namespace llmie {
 
-constexpr int kRouteWarps = 4;
+constexpr int kRouteWarps = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
@@ -20,7 +20,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
                  int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int d, int n_experts, int top) {
   // A block per token: the token's row is staged once as float32, its warps share out the experts, and a warp's lanes
   // take fixed columns of a dot product (four running sums each, added in a fixed order).
-  extern __shared__ float route_smem[];            // [d] the row | [n_experts] the logits
+  extern __shared__ __align__(16) float route_smem[];            // [d] the row | [n_experts] the logits
   float* xs = route_smem;
   float* z = route_smem + d;
   pdl_launch_dependents();
@@ -28,12 +28,28 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* xr = x + (size_t)t * d;
+  const bool vec4 = d % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;
   for (int i = threadIdx.x; i < d; i += blockDim.x) xs[i] = to_f32(xr[i]);
   __syncthreads();
   for (int e = warp; e < n_experts; e += kRouteWarps) {
     const float* wr = w + (size_t)e * d;
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     int i = lane;
+    if (vec4) {
+      // 16 bytes a lane and four such loads in flight: a one-token step has nothing else to hide the latency behind
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const int n4 = d >> 2;
+#pragma unroll 4
+      for (int j = lane; j < n4; j += 32) {
+        const float4 wv = w4[j];
+        const float4 xv = reinterpret_cast<const float4*>(xs)[j];
+        a0 = fmaf(xv.x, wv.x, a0);
+        a1 = fmaf(xv.y, wv.y, a1);
+        a2 = fmaf(xv.z, wv.z, a2);
+        a3 = fmaf(xv.w, wv.w, a3);
+      }
+      i = d;
+    }
     for (; i + 96 < d; i += 128) {
       a0 = fmaf(xs[i], wr[i], a0);
       a1 = fmaf(xs[i + 32], wr[i + 32], a1);

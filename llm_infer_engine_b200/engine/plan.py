@@ -79,8 +79,14 @@ class KernelPlan:
                                      softcap=options.softcap, dist_bias=options.distance_bias,
                                      sink_values=options.sink_values)
             return True
+        if not ctx.decode and scale > 0 and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
+            ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
+                                     kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, scale, window,
+                                     options.keep_first, options.sink, gate, options.softcap, options.distance_bias,
+                                     options.sink_values)
+            return True
         if options.scored:
-            # a cap, a bias by distance or a learned sink: the kernels below do not know them
+            # a cap, a bias by distance or a learned sink: the split-KV kernel below does not know them
             return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
         if ctx.decode and options.plain and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
@@ -90,11 +96,6 @@ class KernelPlan:
                                  n_q, n_kv, head_dim, scale, window, run, n_runs, counters=counters)
             if gate is not None:
                 ops.sigmoid_gate(out, gate)
-            return True
-        if not ctx.decode and scale > 0 and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
-            ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
-                                     kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, scale, window,
-                                     options.keep_first, options.sink, gate)
             return True
         return False
 

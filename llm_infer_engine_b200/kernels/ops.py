@@ -698,6 +698,22 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return out
 
 
+def gemm_skinny_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """out (bfloat16 [batch, N / 2]) = act(x Wg^T) * (x Wu^T) for w = [gate rows; up rows] in one kernel, for a few
+    rows of x; act an ACT_* code."""
+    batch, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (N, K))
+    if act == ACT_NONE or not gemm_skinny_ok(batch, N, K, SKINNY_SWIGLU):
+        raise KernelError(f"gemm_skinny_gated: shape batch={batch}, N={N}, K={K} or activation {act} is not supported")
+    _need(out, "out", torch.bfloat16, (batch, N // 2))
+    _work(_nbytes(x, w, out), 2.0 * batch * N * K)
+    f = _fn("gemm_skinny", "llmie_gemm_skinny_gated", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), batch, N, K, N // 2, int(act), _stream()), "gemm_skinny_gated")
+    return out
+
+
 def gemm_skinny_bias_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                          act: int) -> torch.Tensor:
     """out (bfloat16 [batch, N]) = act(x w^T + bias) in one kernel, for a few rows of x; bias float32 [N] or None."""
@@ -863,7 +879,8 @@ def attention_prefill_tc_supported(head_dim: int, page_size: int, dtype: torch.d
 def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, page_size: int,
                          n_seqs: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
                          window: int = 0, keep_first: int = 0, sink: bool = False,
-                         gate: Optional[torch.Tensor] = None):
+                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                         dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None):
     """Causal attention for runs of new tokens on the tcgen05 tensor cores, K and V read from the
     paged cache by TMA. q, out bfloat16 [T, n_q hd] with sequences packed (cu_q int32 [n + 1]);
     seq_start int32 [n]: tokens each sequence held before this step. The caches' last page must be
@@ -886,6 +903,25 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
     if not scale > 0:
         raise KernelError(f"attention_prefill_tc: the scale must be positive, got {scale}")
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
+    if softcap or dist_bias is not None or sink_values is not None:
+        # the options that change single scores: a cap, a bias by distance [n_q, L], the sink's score per head
+        bias_len = 0
+        if dist_bias is not None:
+            _need(dist_bias, "dist_bias", torch.float32, (n_q, None))
+            bias_len = dist_bias.shape[1]
+        if sink_values is not None:
+            _need(sink_values, "sink_values", torch.float32, (n_q,))
+            sink = True
+        f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc_scored",
+                [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_float,
+                                                  _c_void_p, _c_int, _c_void_p, _c_void_p])
+        _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),
+                 seq_slot.data_ptr(), seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                 k_cache.shape[0], T, n_seqs, max_q_len, n_q, n_kv, head_dim, float(scale), int(window),
+                 int(keep_first), 1 if sink else 0, _ptr(gate), gate_ld, tc_status_word(q.device).data_ptr(),
+                 float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _stream()),
+               "attention_prefill_tc_scored")
+        return out
     f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc",
             [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),

@@ -59,6 +59,17 @@ class Linear:
         ops.gemm_skinny(x, self.weight, h, ops.SKINNY_ADD_F32)
         return True
 
+    def gated(self, x: torch.Tensor, act: int) -> Optional[torch.Tensor]:
+        """For a weight that is [gate rows; up rows]: act(x Wg^T) * (x Wu^T) in one kernel for any activation code,
+        or None when no kernel for this shape exists."""
+        if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+            return None
+        if x.shape[0] > ops.SKINNY_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features,
+                                                                         self.in_features, ops.SKINNY_SWIGLU):
+            return None
+        out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
+        return ops.gemm_skinny_gated(x, self.weight, out, act)
+
     def swiglu(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """For a weight that is [gate rows; up rows]: silu(x Wg^T) * (x Wu^T) in one kernel, or None
         when no kernel for this shape exists."""

@@ -67,8 +67,8 @@ class SwiGLU(FeedForward):
                 ops.norm_gate_swiglu(x.h, x.weight, x.eps, w, act)
             else:
                 x = x.apply()
-        if act is None and self.activation == ops.ACT_SILU:
-            act = self.gate_up.swiglu(x)             # product, activation and gate in one kernel
+        if act is None:                              # product, activation and gate in one kernel
+            act = self.gate_up.swiglu(x) if self.activation == ops.ACT_SILU else self.gate_up.gated(x, self.activation)
         if act is None:
             gu = self.gate_up(x)
             act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
