@@ -1,4 +1,4 @@
-"""A small generation library for one GPU (NVIDIA B200, sm_100a) and the architectures registered in `models/` (Llama, Zemivik).
+"""A small generation library for one GPU (NVIDIA B200, sm_100a) and the architectures registered in `models/` (Llama, Zemivik, Dofipel).
 
     from llm_infer_engine_b200 import Engine, SamplingParams, generate, write_random_model
     engine = Engine("path/to/model_dir", dtype="bfloat16")

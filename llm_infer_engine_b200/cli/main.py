@@ -21,7 +21,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(description="Generation on one B200 for the registered architectures (Llama, Zemivik)")
+    p = argparse.ArgumentParser(description="Generation on one B200 for the registered architectures (Llama, Zemivik, Dofipel)")
     p.add_argument("--env-file", type=str, default=".env", help="Path to .env file, default: .env")
     p.add_argument("--model", type=str, default=None, help="Model folder: config.json, model.safetensors, tokenizer")
     p.add_argument("--tokenizer", type=str, default=None, help="Tokenizer path (also searched for config.json)")

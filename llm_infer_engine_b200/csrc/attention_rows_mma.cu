@@ -8,8 +8,10 @@
 // pairs of one key/value head of one sequence: row r = token * G + head-in-group. A block of eight warps takes 32
 // consecutive rows and walks over the keys its rows may see in tiles of 32 (half a cache page, fetched with cp.async
 // into a two-stage ring):
-//   S = Q K^T      eight 16 x 8 tiles, one per warp, mma.sync m16n8k16 over the head size, into shared memory
-//   softmax        a warp per four rows, a lane per key: scale, cap, bias, mask, running maximum and sum; P in bfloat16
+//   S = Q K^T      mma.sync m16n8k16: a warp takes 16 rows, all 32 keys and a quarter of the head size (partial tiles
+//                  into shared memory, added in the softmax)
+//   softmax        a warp per four rows, eight lanes a row, four keys a lane: scale, cap, bias, mask, running maximum
+//                  and sum; P in bfloat16
 //   O = aO + P V   every warp owns a share of the value columns for all 32 rows (V fragments by ldmatrix.trans)
 // The denominator stays with the warp that owns the row; the final 1 / l (with the sink's term) goes through shared memory.
 #include "common.cuh"
@@ -74,8 +76,8 @@ attention_rows_mma_kernel(const RowsArgs p) {
   __nv_bfloat16* Ks = Qs + kRmRows * kpitch;                                         // [2][32][kpitch]
   __nv_bfloat16* Vs = p.shared_rows ? Ks : Ks + 2 * kRmKeys * kpitch;                // [2][32][vpitch]
   unsigned char* tail = reinterpret_cast<unsigned char*>(Ks + 2 * kRmKeys * kpitch + (p.shared_rows ? 0 : 2 * kRmKeys * vpitch));
-  float* S = reinterpret_cast<float*>(tail);                                         // [32][33]
-  __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(S + kRmRows * 33);             // [32][40]
+  float* S = reinterpret_cast<float*>(tail);                                         // [4][32][33] partial score tiles
+  __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(S + 4 * kRmRows * 33);         // [32][40]
   float* alpha_s = reinterpret_cast<float*>(P + kRmRows * 40);                       // [32]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -123,18 +125,12 @@ attention_rows_mma_kernel(const RowsArgs p) {
   };
   issue(tile_lo, 0);
 
-  // softmax state of the four rows this warp owns (the same in every lane)
-  float m_run[4], l_run[4];
-  int pos_row[4];
-  const float* bias_row[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = r0 + warp * 4 + i;
-    m_run[i] = -INFINITY;
-    l_run[i] = 0.f;
-    pos_row[i] = r < n_rows ? start + r / G : -1;
-    bias_row[i] = (p.dist_bias && r < n_rows) ? p.dist_bias + (size_t)(hk * G + r % G) * p.bias_len : nullptr;
-  }
+  // softmax: a warp owns four rows, eight lanes a row, four keys a lane; the row's state is the same in its eight lanes
+  const int sm_row = warp * 4 + (lane >> 3), sm_key0 = (lane & 7) * 4;
+  float m_run = -INFINITY, l_run = 0.f;
+  const int pos_row = r0 + sm_row < n_rows ? start + (r0 + sm_row) / G : -1;
+  const float* bias_row = (p.dist_bias && r0 + sm_row < n_rows)
+                              ? p.dist_bias + (size_t)(hk * G + (r0 + sm_row) % G) * p.bias_len : nullptr;
   float acc[2][NTW][4];
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
@@ -155,46 +151,73 @@ attention_rows_mma_kernel(const RowsArgs p) {
     __syncthreads();                                      // the tile (and, the first time, Q) is in shared memory
     const __nv_bfloat16* Kt = Ks + stage * kRmKeys * kpitch;
     const __nv_bfloat16* Vt = p.shared_rows ? Kt : Vs + stage * kRmKeys * vpitch;
-    // ---- S = Q K^T, one 16 x 8 tile per warp
+    // ---- S = Q K^T. A warp takes 16 rows, all 32 keys and every fourth step of 16 over the head size, so that a
+    // query fragment it has fetched serves four products; the four partial tiles of a row half meet in the softmax.
     {
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
       const __nv_bfloat16* qa = Qs + (s_mt * 16 + g) * kpitch + 2 * t;
-      const __nv_bfloat16* kb = Kt + (s_nt * 8 + g) * kpitch + 2 * t;
-      for (int ks = 0; ks < p.hd; ks += 16) {
+      const __nv_bfloat16* kb = Kt + g * kpitch + 2 * t;
+      for (int ks = s_nt * 16; ks < p.hd; ks += 64) {
         const unsigned a0 = *reinterpret_cast<const unsigned*>(qa + ks);
         const unsigned a1 = *reinterpret_cast<const unsigned*>(qa + 8 * kpitch + ks);
         const unsigned a2 = *reinterpret_cast<const unsigned*>(qa + ks + 8);
         const unsigned a3 = *reinterpret_cast<const unsigned*>(qa + 8 * kpitch + ks + 8);
-        const unsigned b0 = *reinterpret_cast<const unsigned*>(kb + ks);
-        const unsigned b1 = *reinterpret_cast<const unsigned*>(kb + ks + 8);
-        rm_mma(c, a0, a1, a2, a3, b0, b1);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(kb + nt * 8 * kpitch + ks);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(kb + nt * 8 * kpitch + ks + 8);
+          rm_mma(c[nt], a0, a1, a2, a3, b0, b1);
+        }
       }
-      float* s0 = S + (s_mt * 16 + g) * 33 + s_nt * 8 + 2 * t;
-      s0[0] = c[0];
-      s0[1] = c[1];
-      s0[8 * 33] = c[2];
-      s0[8 * 33 + 1] = c[3];
+      float* s0 = S + s_nt * (kRmRows * 33) + (s_mt * 16 + g) * 33 + 2 * t;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        s0[nt * 8] = c[nt][0];
+        s0[nt * 8 + 1] = c[nt][1];
+        s0[8 * 33 + nt * 8] = c[nt][2];
+        s0[8 * 33 + nt * 8 + 1] = c[nt][3];
+      }
     }
     __syncthreads();
-    // ---- softmax: this warp's four rows, a lane per key
-    const int key = tile * kRmKeys + lane;
+    // ---- softmax of this lane's row over its four keys: scale, cap, bias, mask, running maximum and sum
+    {
+      float sc[4];
+      bool vis[4];
+      float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = warp * 4 + i;
-      float s = S[r * 33 + lane] * p.scale;
-      if (p.softcap > 0.f) s = p.softcap * rm_tanh(s * inv_cap);
-      const int dist = pos_row[i] - key;
-      if (bias_row[i]) s += bias_row[i][min(max(dist, 0), p.bias_len - 1)];
-      const bool vis = dist >= 0 && (p.window == 0 || dist < p.window);
-      s = vis ? s : -INFINITY;
-      const float m_new = fmaxf(m_run[i], warp_max(s));
+      for (int e = 0; e < 4; ++e) {
+        const int col = sm_row * 33 + sm_key0 + e;
+        float x = ((S[col] + S[kRmRows * 33 + col]) + (S[2 * kRmRows * 33 + col] + S[3 * kRmRows * 33 + col])) * p.scale;
+        if (p.softcap > 0.f) x = p.softcap * rm_tanh(x * inv_cap);
+        const int dist = pos_row - (tile * kRmKeys + sm_key0 + e);
+        if (bias_row) x += bias_row[min(max(dist, 0), p.bias_len - 1)];
+        vis[e] = dist >= 0 && (p.window == 0 || dist < p.window);
+        sc[e] = vis[e] ? x : -INFINITY;
+        mx = fmaxf(mx, sc[e]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float m_new = fmaxf(m_run, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float pr = vis ? __expf(s - m_use) : 0.f;
-      const float al = __expf(m_run[i] - m_use);          // 0 while the row has seen no key
-      l_run[i] = l_run[i] * al + warp_sum(pr);
-      m_run[i] = m_new;
-      P[r * 40 + lane] = __float2bfloat16_rn(pr);
-      if (lane == 0) alpha_s[r] = al;
+      float pr[4], sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pr[e] = vis[e] ? __expf(sc[e] - m_use) : 0.f;
+        sum += pr[e];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      const float al = __expf(m_run - m_use);             // 0 while the row has seen no key
+      l_run = l_run * al + sum;
+      m_run = m_new;
+      __nv_bfloat162* pw = reinterpret_cast<__nv_bfloat162*>(P + sm_row * 40 + sm_key0);
+      pw[0] = __floats2bfloat162_rn(pr[0], pr[1]);
+      pw[1] = __floats2bfloat162_rn(pr[2], pr[3]);
+      if ((lane & 7) == 0) alpha_s[sm_row] = al;
     }
     __syncthreads();
     // ---- O = alpha O + P V for this warp's value columns, both 16-row halves
@@ -235,23 +258,20 @@ attention_rows_mma_kernel(const RowsArgs p) {
     __syncthreads();                                      // S, P and this stage may be written again
   }
   // ---- the rows' final factors: 1 / l, with the sink's term in the denominator
-  if (lane == 0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = r0 + warp * 4 + i;
-      float f = 0.f;
-      if (r < n_rows) {
-        float l = l_run[i], m = m_run[i], num = 1.f;
-        if (p.sink) {
-          const float sv = p.sink_vals ? p.sink_vals[hk * G + r % G] : 0.f;
-          const float mx = fmaxf(m, sv);
-          num = m == -INFINITY ? 0.f : __expf(m - mx);
-          l = l * num + __expf(sv - mx);
-        }
-        f = l > 0.f ? num / l : 0.f;
+  if ((lane & 7) == 0) {
+    const int r = r0 + sm_row;
+    float f = 0.f;
+    if (r < n_rows) {
+      float l = l_run, num = 1.f;
+      if (p.sink) {
+        const float sv = p.sink_vals ? p.sink_vals[hk * G + r % G] : 0.f;
+        const float mx = fmaxf(m_run, sv);
+        num = m_run == -INFINITY ? 0.f : __expf(m_run - mx);
+        l = l * num + __expf(sv - mx);
       }
-      alpha_s[warp * 4 + i] = f;
+      f = l > 0.f ? num / l : 0.f;
     }
+    alpha_s[sm_row] = f;
   }
   __syncthreads();
 #pragma unroll
@@ -277,7 +297,7 @@ static size_t rows_smem_bytes(int hd, int hdv, bool shared_rows) {
   const size_t kp = hd + 8, vp = hdv + 8;
   size_t b = (size_t)kRmRows * kp * 2 + 2 * (size_t)kRmKeys * kp * 2;
   if (!shared_rows) b += 2 * (size_t)kRmKeys * vp * 2;
-  return b + kRmRows * 33 * 4 + kRmRows * 40 * 2 + kRmRows * 4;
+  return b + 4 * kRmRows * 33 * 4 + kRmRows * 40 * 2 + kRmRows * 4;
 }
 
 }  // namespace llmie

@@ -1365,7 +1365,7 @@ def attention_rows_mma_supported(head_dim: int, v_head_dim: int, page_size: int,
             or v_head_dim % 8 or v_head_dim > 512 or page_size % 32 or (shared_rows and v_head_dim > head_dim):
         return False
     kp, vp = head_dim + 8, v_head_dim + 8
-    smem = 32 * kp * 2 + 2 * 32 * kp * 2 + (0 if shared_rows else 2 * 32 * vp * 2) + 32 * 33 * 4 + 32 * 40 * 2 + 32 * 4
+    smem = 32 * kp * 2 + 2 * 32 * kp * 2 + (0 if shared_rows else 2 * 32 * vp * 2) + 4 * 32 * 33 * 4 + 32 * 40 * 2 + 32 * 4
     return smem <= 200 * 1024
 
 
