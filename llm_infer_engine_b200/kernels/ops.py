@@ -1213,7 +1213,9 @@ def routed_gemm_nt(a, a_rows, w, out, out_rows, tile_group, n_positions: int, sm
             _need(t, name, torch.int32)
             if t.shape[0] < n_positions:
                 raise KernelError(f"routed_gemm_nt: {name} shorter than the positions")
-    _work(_nbytes(w) + n_positions * (K * a.element_size() + N * out.element_size()),
+    # what is read of the weights is not known on the host: the count assumes the tiles' groups all differ, up to E
+    touched = min(E, n_tiles) / E
+    _work(touched * _nbytes(w) + n_positions * (K * a.element_size() + N * out.element_size()),
           2.0 * n_positions * rows_w * K)
     f = _fn("grouped_gemm", "llmie_grouped_gemm_nt", _GROUPED_ARGS)
     _check(f(a.data_ptr(), lda, 0, _ptr(a_rows), w.data_ptr(), rows_w * K, K, out.data_ptr(), ldc, 0, _ptr(out_rows),
