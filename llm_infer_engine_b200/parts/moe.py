@@ -52,6 +52,7 @@ class RoutedExperts(FeedForward):
                 "activation": str(p.get("shared_activation", name)), "out_float32": True,
                 "names": {"gate": n["gate"], "up": n["up"], "down": n["down"]}}), runtime)
         self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+        self._library = True          # prompts may use the vendor's grouped GEMM until it refuses a shape
 
     def _expert_name(self, e: int, which: str) -> str:
         return f"{self.names['expert'].format(e=e)}.{self.names[which]}"
@@ -108,21 +109,30 @@ class RoutedExperts(FeedForward):
             sorted_token, sorted_pair = index[:n_tiles * tile], index[n_tiles * tile:2 * n_tiles * tile]
             tile_group = index[2 * n_tiles * tile:]
             shared = None
-            if ops.library_grouped_mm_ok(n_pairs, w, self.w_down):
+            if self._library and ops.library_grouped_mm_ok(n_pairs, w, self.w_down):
                 # prompts: each expert's rows side by side, the two products by the library's grouped GEMM
                 extra = torch.empty(E + n_pairs, dtype=torch.int32, device=dev)
                 group_end, pair_pos = extra[:E], extra[E:]
                 ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group, group_end, pair_pos)
                 xs = ops.moe_gather_rows(xin, sorted_token, torch.empty((n_tiles * tile, self.hidden), dtype=w.dtype,
                                                                          device=dev))
-                gu = ops.library_grouped_mm(xs, w, group_end)
-                act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
-                ops.gated_act(gu, act, self.activation)
-                y = ops.library_grouped_mm(act, self.w_down, group_end)
-                if self.shared is not None:
-                    shared = self.shared.forward(x, ctx)
-                out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
-                return ops.moe_combine(y, weights, shared, out, pair_pos)
+                try:
+                    gu = ops.library_grouped_mm(xs, w, group_end)
+                except RuntimeError as exc:
+                    # the library refuses these sizes (it checks before it launches): this library's own routed
+                    # products take them, from now on without asking again
+                    if "CUDA error" in str(exc):
+                        raise
+                    self._library = False
+                    gu = None
+                if gu is not None:
+                    act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
+                    ops.gated_act(gu, act, self.activation)
+                    y = ops.library_grouped_mm(act, self.w_down, group_end)
+                    if self.shared is not None:
+                        shared = self.shared.forward(x, ctx)
+                    out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+                    return ops.moe_combine(y, weights, shared, out, pair_pos)
             ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group)
             # gate and up of every pair's expert with the activation; rows stay in sorted order
             act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
